@@ -1,0 +1,384 @@
+"""Benchmark of the Loopback read path: one step = one K x R pass (N writes, N-1 reads, the whole backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5] [--impl ours|reference]
+
+Prints ONE JSON line. `value` is tokens/s with every input resident in HBM; `e2e` is the same pass with its inputs
+(h0, every block update, every upstream gradient) copied from pinned host memory and its results (last state, query
+gradient) copied back inside the timed region; `roofline` is the backward-read kernel's algorithmic HBM bytes over
+its CUDA-event time against the measured copy bandwidth; `cpu_baseline` is the CPU oracle (a C/OpenMP restatement
+of the reference read, not the product) on a bounded token sample, timed on this host.
+Synthetic data only: h0 ~ N(0,1), updates ~ N(0,0.3^2), queries ~ N(0,0.02^2), upstream gradients ~ N(0,1).
+With --gpus N > 1 (launched by torch.distributed.run) every rank runs the same shard size (weak scaling); the only
+exchange is one all-reduce of the (N-1) x d query gradient per pass.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: d, K, R, batch, seq, storage dtype, backward?
+    "cfg2": dict(d=1024, K=4, R=6, b=8, t=4096, dtype="bf16", backward=True),
+    "cfg3": dict(d=1536, K=6, R=4, b=16, t=4096, dtype="bf16", backward=True),
+    "cfg4": dict(d=3072, K=8, R=3, b=32, t=8192, dtype="bf16", backward=True),
+    "cfg5": dict(d=2048, K=5, R=16, b=64, t=1, dtype="bf16", backward=False),
+}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_units(N: int, backward: bool) -> int:
+    """Row-vector transfers per token of one pass, in units of d * elem bytes: writes 3N; reads S + 2(N-1);
+    backward S (V) + 2S - N (dV read + write, the first backward only writes) + (N-1) (g) + 2N (dx = -g)."""
+    S = N * (N + 1) // 2 - 1
+    fwd = 3 * N + S + 2 * (N - 1)
+    return fwd + (S + 2 * S - N + (N - 1) + 2 * N if backward else 0)
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+        return False
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [nm for k, nm in enumerate(names) if any(len(r) >= 6 and r[2 + k].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# the reference arm / CPU baseline: the CPU oracle on a bounded token sample (never part of the measured product)
+# ------------------------------------------------------------------------------------------------------------------
+def cpu_pass_tokens_per_s(w, sample_tokens: int, repeats: int, warmup: int):
+    import numpy as np
+
+    from oracle import c_oracle as CO
+    CO.build()
+    N, d = w["K"] * w["R"], w["d"]
+    rng = np.random.default_rng(0)
+    h0 = rng.standard_normal((sample_tokens, d), dtype=np.float32)
+    D = rng.standard_normal((N, sample_tokens, d), dtype=np.float32) * np.float32(0.3)
+    Q = rng.standard_normal((N - 1, d), dtype=np.float32) * np.float32(0.02)
+    G = rng.standard_normal((N, sample_tokens, d), dtype=np.float32) if w["backward"] else None
+    bf16 = w["dtype"] == "bf16"
+    if bf16:
+        h0, D = CO.round_bf16(h0), CO.round_bf16(D)
+    times = []
+    for k in range(warmup + repeats):
+        t0 = time.perf_counter()
+        CO.chain(h0, D, Q, G, w["K"], w["R"], 0.75, 1e-6, bf16)
+        if k >= warmup:
+            times.append(time.perf_counter() - t0)
+    return sample_tokens / statistics.median(times), statistics.median(times), CO.num_threads()
+
+
+def run_reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = min(w["b"] * w["t"], 2048)
+    tps, sec, cores = cpu_pass_tokens_per_s(w, sample, max(1, args.steps), max(1, args.warmup))
+    line = {
+        "impl": "reference", "metric": "loopback_read_fwd_bwd_tokens_per_s" if w["backward"] else "loopback_read_fwd_tokens_per_s",
+        "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: d={w['d']} K={w['K']} R={w['R']} storage={w['dtype']}",
+                   "sample": f"{sample} tokens of the {w['b'] * w['t']}-token workload (the read is token-parallel)"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} tokens, one K x R pass per step, C/OpenMP restatement of the reference read"},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# the measured arm
+# ------------------------------------------------------------------------------------------------------------------
+class Pass:
+    """One K x R pass through the public entry points (DattnStack.write + LoopDeltaAttnRes.combine + autograd)."""
+
+    def __init__(self, w, device, seed):
+        import torch
+
+        from loopback_b200.cell import LoopDeltaAttnRes
+        self.torch, self.w, self.dev = torch, w, device
+        self.N, self.d, self.b, self.t = w["K"] * w["R"], w["d"], w["b"], w["t"]
+        self.dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+        g = torch.Generator(device=device).manual_seed(seed)
+        shape = (self.b, self.t, self.d)
+        self.cell = LoopDeltaAttnRes(self.d, w["R"], w["K"], beta=0.75, eps=1e-6).to(device)
+        with torch.no_grad():
+            self.cell.query.copy_(torch.randn(self.N - 1, self.d, device=device, generator=g) * 0.02)
+        self.h0 = torch.randn(shape, device=device, generator=g).to(self.dtype).requires_grad_(w["backward"])
+        # pools of 3 update / gradient tensors, cycled over the steps (kernel cost does not depend on the values)
+        self.D = [(torch.randn(shape, device=device, generator=g) * 0.3).to(self.dtype) for _ in range(3)]
+        self.G = [torch.randn(shape, device=device, generator=g).to(self.dtype) for _ in range(3)] if w["backward"] else None
+
+    def run(self, h0=None, D=None, G=None):
+        torch, cell, K = self.torch, self.cell, self.w["K"]
+        h0 = self.h0 if h0 is None else h0
+        D = self.D if D is None else D
+        G = self.G if G is None else G
+        backward = self.w["backward"]
+        cell.query.grad = None
+        h0.grad = None
+        stack = cell.new_stack((self.b, self.t, self.d), self.dtype, self.dev, scores=True)
+        x, deltas, keys, coeffs, prior, outs = h0, [], [], None, None, []
+        with torch.set_grad_enabled(backward):
+            for s in range(self.N):
+                l, blk = divmod(s, K)
+                hs = x + D[s % len(D)]                       # the "block": harness cost, inside the timed region
+                deltas.append(stack.write(s, hs, x))
+                x, coeffs, prior = cell.combine(hs, h0, deltas, coeffs, prior, l, blk, keys=keys, stack=stack)
+                outs.append(x)
+            if backward:
+                torch.autograd.backward(outs, [G[s % len(G)] for s in range(self.N)])
+        return x
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on small cases)")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        w["b"], w["t"] = 1, args.tokens
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+
+    import loopback_b200._lib as L
+    from loopback_b200 import fused_dattn as FD
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L.lib()
+
+    N, d = w["K"] * w["R"], w["d"]
+    n_tok = w["b"] * w["t"]
+    elem = 2 if w["dtype"] == "bf16" else 4
+    P = Pass(w, dev, seed=rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_pass(**kw):
+        out = P.run(**kw)
+        if w["backward"] and world > 1:
+            dist.all_reduce(P.cell.query.grad)             # the (N-1) x d query gradient: the only exchange
+        return out
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident timing, with per-launch events on the dominant kernels -------------------------------
+    for _ in range(args.warmup):
+        one_pass()
+    launches = []
+
+    class Timer:
+        def __init__(self, kind, n, accum):
+            self.rec = (kind, n, accum, torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+
+        def __enter__(self):
+            self.rec[3].record()
+
+        def __exit__(self, *a):
+            self.rec[4].record()
+            launches.append(self.rec)
+            return False
+
+    FD.LAUNCH_TIMER = Timer
+    count0 = L.LAUNCHES["count"]
+    with ClockSampler(local) as clocks:
+        total_ms = timed(one_pass, args.steps)
+    gpu_launches = (L.LAUNCHES["count"] - count0) // args.steps
+    FD.LAUNCH_TIMER = None
+    assert FD.device_error() == 0, "a kernel gave up a bounded wait"
+    ms_per_step = total_ms / args.steps
+    value = world * n_tok / (ms_per_step * 1e-3)
+
+    # ---- roofline of the dominant kernel: algorithmic bytes of its launches over their event time -------------
+    peak, peak_kind = measured_peak()
+    per_kind = {}
+    for kind, n, accum, a, b_ in launches:
+        ms = a.elapsed_time(b_)
+        if kind == "read_bwd":
+            units = n + (2 * n if accum else n) + 1            # V, dV (read+write or write), g
+        elif kind == "read_fwd":
+            units = n + 2                                       # V, base, out
+        else:
+            units = 3                                           # write: h, x, V[s]
+        acc = per_kind.setdefault(kind, [0.0, 0.0, 0])
+        acc[0] += units * n_tok * d * elem
+        acc[1] += ms * 1e-3
+        acc[2] += 1
+    dominant = max(per_kind, key=lambda k: per_kind[k][1]) if per_kind else None
+    roofline = None
+    kernels = {}
+    for kind, (by, sec, cnt) in per_kind.items():
+        kernels[kind] = {"launches_per_step": cnt // args.steps, "ms_per_step": sec * 1e3 / args.steps,
+                         "achieved_gbs": by / sec / 1e9, "frac": by / sec / 1e9 / peak}
+    if dominant:
+        by, sec, cnt = per_kind[dominant]
+        roofline = {"bound": "hbm", "kernel": dominant, "achieved": by / sec / 1e9, "peak": peak, "unit": "GB/s",
+                    "frac": by / sec / 1e9 / peak, "peak_source": peak_kind, "traffic": None,
+                    "bytes_per_launch_avg": by / cnt, "ms_per_launch_avg": sec * 1e3 / cnt}
+    pass_units = algorithmic_units(N, w["backward"])
+    pass_gbs = pass_units * n_tok * d * elem / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: host buffers in, results out, inside the timed region ------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        shape = (w["b"], w["t"], d)
+        host_h0 = torch.randn(shape).to(P.dtype).pin_memory()
+        host_D = [(torch.randn(shape) * 0.3).to(P.dtype).pin_memory() for _ in range(2)]
+        host_G = [torch.randn(shape).to(P.dtype).pin_memory() for _ in range(2)] if w["backward"] else None
+        out_host = torch.empty(shape, dtype=P.dtype).pin_memory()
+        dq_host = torch.empty((N - 1, d), dtype=torch.float32).pin_memory()
+        copy_stream = torch.cuda.Stream(device=dev)
+        h2d = (1 + N + (N if w["backward"] else 0)) * n_tok * d * elem
+        d2h = n_tok * d * elem + ((N - 1) * d * 4 if w["backward"] else 0)
+
+        class HostFed:
+            """Per-step inputs staged from pinned host memory on a copy stream, two steps ahead of the compute."""
+
+            def __init__(self, pool):
+                self.pool, self.ring, self.k = pool, [], 0
+
+            def __len__(self):
+                return 1 << 30
+
+            def __getitem__(self, s):
+                src = self.pool[s % len(self.pool)]
+                with torch.cuda.stream(copy_stream):
+                    buf = torch.empty(shape, dtype=P.dtype, device=dev)
+                    buf.copy_(src, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(copy_stream)
+                torch.cuda.current_stream().wait_event(ev)
+                buf.record_stream(torch.cuda.current_stream())
+                return buf
+
+        def e2e_pass():
+            h0d = torch.empty(shape, dtype=P.dtype, device=dev)
+            h0d.copy_(host_h0, non_blocking=True)
+            h0d.requires_grad_(w["backward"])
+            out = one_pass(h0=h0d, D=HostFed(host_D), G=HostFed(host_G) if w["backward"] else None)
+            out_host.copy_(out.detach(), non_blocking=True)
+            if w["backward"]:
+                dq_host.copy_(P.cell.query.grad, non_blocking=True)
+
+        for _ in range(2):
+            e2e_pass()
+        e2e_steps = max(2, min(args.steps, 5))
+        e2e_ms = timed(e2e_pass, e2e_steps) / e2e_steps
+        e2e = {"value": world * n_tok / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+    # ---- CPU baseline (rank 0, single-GPU runs only) --------------------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample = min(n_tok, 2048)
+        tps, sec, cores = cpu_pass_tokens_per_s(w, sample, repeats=3, warmup=1)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": f"{sample} tokens of the workload, one K x R pass, {sec:.2f} s per pass; "
+                         "C/OpenMP restatement of the reference read"}
+
+    if rank == 0:
+        line = {
+            "metric": "loopback_read_fwd_bwd_tokens_per_s" if w["backward"] else "loopback_read_fwd_tokens_per_s",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: d={d} K={w['K']} R={w['R']} B={w['b']} T={w['t']} per GPU, "
+                                   f"storage={w['dtype']}, fp32 arithmetic, stack + cached scores, "
+                                   f"{'forward+backward' if w['backward'] else 'forward only'}",
+                       "tokens_per_gpu": n_tok, "l2": "inputs larger than L2 (the update stack alone is "
+                                                     f"{N * n_tok * d * elem / 2**20:.0f} MiB per GPU)",
+                       "parallelism": f"tokens x{world}" if world > 1 else "single GPU",
+                       "pass_algorithmic_gbs": pass_gbs, "pass_frac_of_peak": pass_gbs / peak, "kernels": kernels},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

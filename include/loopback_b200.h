@@ -1,0 +1,121 @@
+/*
+ * loopback_b200 -- C ABI of the B200 (sm_100a) kernels for Loopback's depth-attention residual read.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the CUDA stream it is given
+ * (a cudaStream_t passed as void*; NULL = the default stream), never synchronises, never allocates device memory,
+ * and returns LB_OK or a negative LB_ERR_* code; lb_last_error_string() describes the last failure of the calling
+ * thread. There is no CPU fallback: on a machine without an sm_100 GPU every compute call fails with LB_ERR_CUDA.
+ *
+ * Shapes: n_tok = batch * sequence tokens; d = model width; N = K * R block applications ("steps") of one forward
+ * pass; NQ = N - 1 read queries; a read at step s sees n = s + 1 stored updates and uses query row s - 1.
+ * dtype selects the storage type of activations (LB_DTYPE_BF16 or LB_DTYPE_F32); all arithmetic is fp32.
+ * Constraints: d * sizeof(element) is a multiple of 16 and at most 16384 bytes; activation pointers are 16-byte
+ * aligned; n <= LB_MAX_SOURCES.
+ *
+ * Layouts (row-major, contiguous):
+ *   V, dV   [N][n_tok][d]   storage dtype      the stack of updates / their gradients
+ *   R, dR   [N][n_tok]      fp32               key scales rsqrt(mean(v^2) + eps) / their gradients
+ *   DOTS    [NQ][N][n_tok]  fp32               cached scores q_j . V[s, t, :]; private to this library
+ *   cbar, TC, LG, dcbar, gt  [n_tok][n] fp32;  LSE, LSE0 [n_tok] fp32;  c0 [n] fp32;  Q [NQ][d] fp32
+ *
+ * The reference interface each entry point replaces is cited by file:line of the reference project
+ * (fused_dattn.py is the Triton implementation, looped_transformer.py the model with the reference read).
+ */
+#ifndef LOOPBACK_B200_H
+#define LOOPBACK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LB_VERSION 1
+
+#define LB_DTYPE_F32 0
+#define LB_DTYPE_BF16 1
+
+#define LB_MAX_SOURCES 128
+
+#define LB_OK 0
+#define LB_ERR_ARG (-1)          /* null pointer, negative size, n out of range ... */
+#define LB_ERR_ALIGN (-2)        /* pointer or row size not 16-byte aligned */
+#define LB_ERR_UNSUPPORTED (-3)  /* shape outside what the kernels cover (d too large, n > LB_MAX_SOURCES) */
+#define LB_ERR_CUDA (-4)         /* a CUDA runtime/driver call failed (includes: no sm_100 device) */
+#define LB_ERR_DEVICE (-5)       /* a kernel reported a bounded wait that ran out (lb_device_error) */
+
+/* Library version (LB_VERSION of the build). */
+int lb_version(void);
+
+/* Message of the last error returned to the calling thread ("" if none). The pointer stays valid until the
+ * thread's next failing call. */
+const char *lb_last_error_string(void);
+
+/* Reads (and, if clear != 0, resets) the current device's error word. 0 = no kernel gave up a wait; otherwise the
+ * code of the first wait that ran out. SYNCHRONISES the device; meant for tests and for the end of a step. */
+int lb_device_error(int clear);
+
+/* Tuning knobs ("fwd_stages", "bwd_stages", "fwd_fr", "grid_cap"); value 0 restores the default.
+ * Returns LB_ERR_ARG for an unknown name. */
+int lb_set_option(const char *name, int value);
+
+/* Update write: V[s] = round(h - x); R[s] = key scale of the rounded update; if Q != NULL also the cached scores
+ * DOTS[j][s][:] = Q[j] . V[s] for the queries j >= max(s - 1, 0) (the reads that will see update s).
+ * R may be NULL (then only V[s] is written and Q is ignored).
+ * Replaces DattnStack.write / _WriteDelta.forward and the kernel _write_stk_kernel (fused_dattn.py:561-585,
+ * :663-691) and, when R is requested without Q, the scale kernel used by DattnStack.rstd (fused_dattn.py:698-708). */
+int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, float *DOTS, int64_t n_tok, int d, int N,
+             int NQ, int s, float eps, int dtype, void *stream);
+
+/* Gradient of the write for the block input: dx = -g (dh is g itself).
+ * Replaces _WriteDelta.backward (fused_dattn.py:693-695). */
+int lb_write_bwd_dx(const void *g, void *dx, int64_t n_elem, int dtype, void *stream);
+
+/* Key scale of a free-standing update: r[t] = rsqrt(mean(x[t,:]^2) + eps).
+ * Replaces rstd / _Rstd.forward and _rstd_fwd_kernel (fused_dattn.py:206-215, :232-243, :257-261). */
+int lb_rstd_fwd(const void *x, float *r, int64_t n_tok, int d, float eps, int dtype, void *stream);
+
+/* Gradient of the key scale, written: gx = gr * (-r^3 / d) * x.
+ * Replaces _Rstd.backward and _rstd_bwd_kernel (fused_dattn.py:218-229, :245-254). */
+int lb_rstd_bwd(const void *x, const float *r, const float *gr, void *gx, int64_t n_tok, int d, int dtype,
+                void *stream);
+
+/* Gradient of the key scale, accumulated: dv = round(dv + round(gr * (-r^3 / d) * x)) in the storage dtype.
+ * Replaces _RstdStk.backward and _rstd_bwd_acc_kernel (fused_dattn.py:539-552, :711-722). */
+int lb_rstd_bwd_acc(const void *x, const float *r, const float *gr, void *dv, int64_t n_tok, int d, int dtype,
+                    void *stream);
+
+/* Scores of one query against the first n updates of a stack whose writes did not cache them:
+ * dots[i][t] = q . V[i, t, :], dots laid out [N][n_tok] (one query block of DOTS, or caller scratch).
+ * Replaces the score half of the online read kernel _dattn_fwd_stk_kernel (fused_dattn.py:426-433). */
+int lb_scores(const void *V, const float *q, float *dots, int64_t n_tok, int d, int N, int n, int dtype, void *stream);
+
+/* Forward read at step s = n - 1 from cached scores (query row qi of DOTS):
+ *   l_i = DOTS[qi][i] * R[i] / sqrt(d) + log(max(c0_i, 1e-8));  p = softmax(l);  p0 = softmax(log-prior)
+ *   TC_i = c0_i + sum(c0) * (p_i - p0_i);   out = base + sum_i (TC_i - cbar_i) * V[i]
+ * Saves LG (= l), LSE, LSE0 for the backward when they are non-NULL (all three or none).
+ * Replaces FusedDattnReadStk.forward with its host preparation and the kernels _dattn_fwd_dots_kernel /
+ * _dattn_fwd_stk_kernel (fused_dattn.py:729-759, :588-625, :410-456); the reference read it reproduces is
+ * LoopDeltaAttnRes.combine (looped_transformer.py:410-424). */
+int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const void *base, const float *cbar,
+                const float *c0, void *out, float *TC, float *LG, float *LSE, float *LSE0, int64_t n_tok, int d, int N,
+                int n, int dtype, void *stream);
+
+/* Bytes of scratch lb_read_bwd needs for the per-CTA partial rows of the query gradient (depends on d only). */
+size_t lb_read_bwd_scratch_bytes(int d);
+
+/* Backward read: from g = dL/dout [n_tok][d] and gt = dL/dTC [n_tok][n] (NULL = zeros) and the forward's saves,
+ *   dq [d] (written), dcbar [n_tok][n] (written), dV[i], dR[i] for i < n (written if accum == 0, else added into,
+ *   with the storage-dtype rounding of an in-place autograd add). dL/dbase is g itself.
+ * `scratch` must hold lb_read_bwd_scratch_bytes(d) bytes; it is fully overwritten.
+ * Replaces FusedDattnReadStk.backward, the kernels _dattn_bwd1_stk_kernel / _dattn_bwd2_stk_kernel and the torch
+ * reduction of the query-gradient partials (fused_dattn.py:761-793, :459-536). */
+int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
+                const float *cbar, const float *c0, const float *LG, const float *LSE, const float *LSE0, float *dcbar,
+                float *dq, void *scratch, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOOPBACK_B200_H */

@@ -1,0 +1,98 @@
+"""The Loopback read cell on top of the CUDA kernels: a host-side mirror of the reference's `LoopDeltaAttnRes`.
+
+Same constructor, parameter (`query`, (K R - 1, d), zero-initialised) and `combine` contract as the reference cell
+(looped_transformer.py:334-424; the trainer model's copy adds the `stack=` argument), so a model loop written for the
+reference runs unchanged.  Unlike the reference there is one path only -- the fused kernels -- and no environment
+switch: inputs the kernels cannot take raise instead of silently taking an eager read.
+
+    h_{s+1} = h_0 + sum_{i<=s} c_{s,i} d_i,    c_{s,i} = B_s softmax_i(q_s . rmsnorm(d_i) / sqrt(d) + log c0_{s,i})
+    c0_{s,i} = lambda^(floor((s+1)/K) - floor(i/K)),   B_s = sum_i c0_{s,i},   lambda = 1 - beta
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from . import fused_dattn as FD
+
+
+class LoopDeltaAttnRes(nn.Module):
+    def __init__(self, hidden_size: int, num_loops: int, num_blocks: int, beta: float = 0.75, eps: float = 1e-6):
+        super().__init__()
+        if num_loops < 1 or num_blocks < 1:
+            raise ValueError(f"delta_attnres needs positive num_loops/num_blocks, got {num_loops}/{num_blocks}")
+        if not 0.0 <= float(beta) < 1.0:
+            raise ValueError(f"delta_attnres needs 0 <= beta < 1, got {beta}")
+        self.dim = int(hidden_size)
+        self.num_loops = int(num_loops)
+        self.num_blocks = int(num_blocks)
+        self.num_steps = self.num_loops * self.num_blocks
+        self.beta = float(beta)
+        self.eps = float(eps)
+        self.query = nn.Parameter(torch.zeros(self.num_steps - 1, self.dim))
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        with torch.no_grad():
+            self.query.zero_()
+
+    def new_stack(self, shape, dtype, device, scores: bool = True) -> FD.DattnStack:
+        """The per-forward storage the model creates before its loop over the shared blocks (the trainer model's
+        forward does this inline); `scores` caches each update's scores at its write (LOOP_DATTN_DOTS)."""
+        return FD.DattnStack(self.num_steps, tuple(shape), dtype, device, query=self.query if scores else None,
+                             eps=self.eps)
+
+    def combine(self, proposal, h0, deltas, coeffs, prior_coeffs, loop_idx, block_idx, keys=None, stack=None):
+        """One read after application `block_idx` of iteration `loop_idx`.
+
+        proposal  the block output (b, t, d);  h0 the loop input;  deltas the updates stored so far (this one last);
+        coeffs    the coefficients the previous read installed, (b, t, n - 1) fp32, None at the first read;
+        prior_coeffs  the previous read's prior (n - 1,) fp32, None at the first read;
+        keys      optional caller-owned cache of the updates' key scales, extended here by one;
+        stack     the pass's DattnStack when the updates are its slices (the fast path).
+        Returns (next state, installed coefficients, this read's prior)."""
+        if not 0 <= block_idx < self.num_blocks:
+            raise ValueError(f"delta_attnres block_idx={block_idx}, need [0,{self.num_blocks})")
+        step = loop_idx * self.num_blocks + block_idx
+        if step >= self.num_steps:
+            raise ValueError(f"delta_attnres step {step} exceeds constructed depth {self.num_steps}")
+        if len(deltas) != step + 1:
+            raise ValueError(f"delta_attnres step {step} received {len(deltas)} deltas, expected {step + 1}")
+
+        closes_iteration = block_idx == self.num_blocks - 1
+        base = proposal + self.beta * (h0 - proposal) if closes_iteration else proposal
+        ones_tok = torch.ones(*proposal.shape[:-1], 1, device=proposal.device, dtype=torch.float32)
+        ones_one = torch.ones(1, device=proposal.device, dtype=torch.float32)
+        cbar = ones_tok if coeffs is None else torch.cat((coeffs, ones_tok), dim=-1)
+        c0 = ones_one if prior_coeffs is None else torch.cat((prior_coeffs, ones_one), dim=-1)
+        if closes_iteration:
+            lam = 1.0 - self.beta
+            cbar, c0 = lam * cbar, lam * c0
+
+        if stack is not None:
+            if keys is not None and len(keys) < len(deltas):
+                keys.append(stack.rstd(step, deltas[-1], self.eps))
+            if step == 0:
+                return base, cbar, c0
+            scales = keys if keys is not None else [FD._alias(stack.R, i) for i in range(len(deltas))]
+            out, tc = FD.FusedDattnReadStk.apply(stack, step, self.query[step - 1], base.contiguous(), cbar, c0,
+                                                 *deltas, *scales)
+            return out, tc, c0
+
+        if keys is not None and len(keys) < len(deltas):
+            keys.append(FD.rstd(deltas[-1], self.eps))
+        if step == 0:
+            return base, cbar, c0
+        scales = keys if keys is not None else [FD.rstd(v, self.eps) for v in deltas]
+        if not FD.fused_read_supported(base, deltas, scales, cbar):
+            raise RuntimeError("delta_attnres: the fused read does not support this layout "
+                               "(CUDA, contiguous, one dtype in {bf16, fp32}, row size a multiple of 16 bytes)")
+        out, tc = FD.FusedDattnRead.apply(self.query[step - 1], base, cbar, c0, *deltas, *scales)
+        return out, tc, c0
+
+
+def install(reference_model_module, fused_module=FD) -> None:
+    """Make a reference model module (the port `looped_transformer` or the trainer's
+    `modeling_looped_transformer`) use this package as its fused read: it sets the module-level cache its
+    `_fused_dattn()` consults, exactly what the reference's own tests do to switch paths."""
+    reference_model_module._FUSED_DATTN = fused_module

@@ -1,0 +1,350 @@
+// C-ABI layer: argument checks, tile-shape selection, TMA descriptors, launches. See include/loopback_b200.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include <cudaTypedefs.h>
+
+#include "../../include/loopback_b200.h"
+#include "lb_common.cuh"
+#include "lb_kernels.h"
+
+// one error word per device: the first bounded wait of any kernel that runs out records its code here
+__device__ int g_lb_device_error = 0;
+
+namespace {
+
+constexpr int kMaxGrid = 304;                 // rows of the query-gradient scratch (>= 2 CTAs per SM on 148 SMs)
+constexpr size_t kMaxSmem = 227 * 1024;
+
+thread_local std::string t_err;
+
+int fail(int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    t_err = buf;
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+    return fail(LB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+struct Options {
+    int fwd_stages = 0, bwd_stages = 0, fwd_fr = 0, grid_cap = 0;
+} g_opt;
+
+struct DeviceInfo {
+    int sms = 0;
+    int cc_major = 0;
+    int *err_word = nullptr;
+    bool ok = false;
+};
+
+int device_info(DeviceInfo *out) {
+    static std::mutex mu;
+    static DeviceInfo cache[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(LB_ERR_CUDA, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cache[dev].ok) {
+        DeviceInfo di;
+        if ((e = cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+            return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
+        if ((e = cudaDeviceGetAttribute(&di.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+            return cuda_fail(e, "cudaDeviceGetAttribute(cc major)");
+        if (di.cc_major != 10)
+            return fail(LB_ERR_CUDA, "device %d has compute capability %d.x; this library is built for sm_100a only",
+                        dev, di.cc_major);
+        if ((e = cudaGetSymbolAddress(reinterpret_cast<void **>(&di.err_word), g_lb_device_error)) != cudaSuccess)
+            return cuda_fail(e, "cudaGetSymbolAddress(device error word)");
+        di.ok = true;
+        cache[dev] = di;
+    }
+    *out = cache[dev];
+    return LB_OK;
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    });
+    return fn;
+}
+
+// A tiled descriptor over [outer][n_tok][d] (outer == 0: rank 2), box = 512 bytes x box_tok tokens.
+int make_map(CUtensorMap *m, const void *base, int dtype, long long n_tok, int d, int outer, int box_tok) {
+    auto fn = encode_fn();
+    if (!fn) return fail(LB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
+    const cuuint32_t rank = outer > 0 ? 3 : 2;
+    cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)n_tok, (cuuint64_t)(outer > 0 ? outer : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)d * elem, (cuuint64_t)d * elem * (cuuint64_t)n_tok};
+    cuuint32_t box[3] = {(cuuint32_t)(lb::kChunkBytes / elem), (cuuint32_t)box_tok, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, dtype == LB_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                    rank, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return LB_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_common(long long n_tok, int d, int dtype) {
+    if (dtype != LB_DTYPE_BF16 && dtype != LB_DTYPE_F32) return fail(LB_ERR_ARG, "dtype %d is neither LB_DTYPE_F32 nor LB_DTYPE_BF16", dtype);
+    if (n_tok < 0 || d <= 0) return fail(LB_ERR_ARG, "n_tok=%lld, d=%d: sizes must be positive", n_tok, d);
+    if (n_tok >= (1LL << 31)) return fail(LB_ERR_UNSUPPORTED, "n_tok=%lld does not fit the 32-bit TMA coordinates", n_tok);
+    const long long row = (long long)d * (dtype == LB_DTYPE_BF16 ? 2 : 4);
+    if (row % 16 != 0) return fail(LB_ERR_ALIGN, "row size %lld bytes (d=%d) is not a multiple of 16", row, d);
+    if (row > 32 * lb::kChunkBytes) return fail(LB_ERR_UNSUPPORTED, "row size %lld bytes exceeds the supported 16384", row);
+    return LB_OK;
+}
+
+int chunks_of(int d, int dtype) {
+    const int row = d * (dtype == LB_DTYPE_BF16 ? 2 : 4);
+    return (row + lb::kChunkBytes - 1) / lb::kChunkBytes;
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+int lb_version(void) { return LB_VERSION; }
+
+const char *lb_last_error_string(void) { return t_err.c_str(); }
+
+int lb_device_error(int clear) {
+    int v = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+    e = cudaMemcpyFromSymbol(&v, g_lb_device_error, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyFromSymbol(device error word)");
+    if (clear && v != 0) {
+        int z = 0;
+        e = cudaMemcpyToSymbol(g_lb_device_error, &z, sizeof(int));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol(device error word)");
+    }
+    if (v != 0) fail(LB_ERR_DEVICE, "a kernel gave up a bounded wait (code %d)", v);
+    return v;
+}
+
+int lb_set_option(const char *name, int value) {
+    if (!name) return fail(LB_ERR_ARG, "option name is NULL");
+    if (!strcmp(name, "fwd_stages")) g_opt.fwd_stages = value;
+    else if (!strcmp(name, "bwd_stages")) g_opt.bwd_stages = value;
+    else if (!strcmp(name, "fwd_fr")) g_opt.fwd_fr = value;
+    else if (!strcmp(name, "grid_cap")) g_opt.grid_cap = value;
+    else return fail(LB_ERR_ARG, "unknown option '%s'", name);
+    return LB_OK;
+}
+
+int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, float *DOTS, int64_t n_tok, int d, int N,
+             int NQ, int s, float eps, int dtype, void *stream) {
+    int rc = check_common(n_tok, d, dtype);
+    if (rc) return rc;
+    if (!h || !x || !V) return fail(LB_ERR_ARG, "lb_write: h, x and V must be non-NULL");
+    if (N <= 0 || s < 0 || s >= N) return fail(LB_ERR_ARG, "lb_write: step %d outside [0, %d)", s, N);
+    if (Q && (!DOTS || !R || NQ < 0 || NQ > N)) return fail(LB_ERR_ARG, "lb_write: scores need R, DOTS and 0 <= NQ <= N");
+    if (!aligned16(h) || !aligned16(x) || !aligned16(V) || (Q && !aligned16(Q)))
+        return fail(LB_ERR_ALIGN, "lb_write: h, x, V and Q must be 16-byte aligned");
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    const long long elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
+    lb::WriteParams p;
+    p.h = h; p.x = x;
+    p.v = static_cast<char *>(V) + (long long)s * n_tok * d * elem;
+    p.r = R ? R + (long long)s * n_tok : nullptr;
+    p.Q = (Q && R) ? Q : nullptr;
+    p.j0 = s > 0 ? s - 1 : 0;
+    p.nq = p.Q ? NQ - p.j0 : 0;
+    if (p.nq <= 0) { p.nq = 0; p.Q = nullptr; }
+    p.dots_s = DOTS ? DOTS + (long long)s * n_tok : nullptr;
+    p.dots_qstride = (long long)N * n_tok;
+    p.n_tok = n_tok; p.d = d; p.eps = eps;
+    cudaError_t e = lb::launch_write(dtype, p, di.sms, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_write launch");
+}
+
+int lb_write_bwd_dx(const void *g, void *dx, int64_t n_elem, int dtype, void *stream) {
+    if (dtype != LB_DTYPE_BF16 && dtype != LB_DTYPE_F32) return fail(LB_ERR_ARG, "bad dtype %d", dtype);
+    if (!g || !dx || n_elem < 0) return fail(LB_ERR_ARG, "lb_write_bwd_dx: NULL pointer or negative size");
+    if (!aligned16(g) || !aligned16(dx) || (n_elem * (dtype == LB_DTYPE_BF16 ? 2 : 4)) % 16)
+        return fail(LB_ERR_ALIGN, "lb_write_bwd_dx: pointers and byte size must be multiples of 16");
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc) return rc;
+    cudaError_t e = lb::launch_neg(dtype, g, dx, n_elem, di.sms, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_write_bwd_dx launch");
+}
+
+int lb_rstd_fwd(const void *x, float *r, int64_t n_tok, int d, float eps, int dtype, void *stream) {
+    int rc = check_common(n_tok, d, dtype);
+    if (rc) return rc;
+    if (!x || !r) return fail(LB_ERR_ARG, "lb_rstd_fwd: NULL pointer");
+    if (!aligned16(x)) return fail(LB_ERR_ALIGN, "lb_rstd_fwd: x must be 16-byte aligned");
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    cudaError_t e = lb::launch_rstd_fwd(dtype, x, r, n_tok, d, eps, di.sms, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_rstd_fwd launch");
+}
+
+static int rstd_bwd_common(const void *x, const float *r, const float *gr, void *gx, int64_t n_tok, int d, int dtype,
+                           int mode, void *stream) {
+    int rc = check_common(n_tok, d, dtype);
+    if (rc) return rc;
+    if (!x || !r || !gr || !gx) return fail(LB_ERR_ARG, "lb_rstd_bwd: NULL pointer");
+    if (!aligned16(x) || !aligned16(gx)) return fail(LB_ERR_ALIGN, "lb_rstd_bwd: x and gx must be 16-byte aligned");
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    cudaError_t e = lb::launch_rstd_bwd(dtype, x, r, gr, gx, n_tok, d, mode, di.sms, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_rstd_bwd launch");
+}
+
+int lb_rstd_bwd(const void *x, const float *r, const float *gr, void *gx, int64_t n_tok, int d, int dtype, void *stream) {
+    return rstd_bwd_common(x, r, gr, gx, n_tok, d, dtype, 0, stream);
+}
+
+int lb_rstd_bwd_acc(const void *x, const float *r, const float *gr, void *dv, int64_t n_tok, int d, int dtype,
+                    void *stream) {
+    return rstd_bwd_common(x, r, gr, dv, n_tok, d, dtype, 1, stream);
+}
+
+int lb_scores(const void *V, const float *q, float *dots, int64_t n_tok, int d, int N, int n, int dtype, void *stream) {
+    int rc = check_common(n_tok, d, dtype);
+    if (rc) return rc;
+    if (!V || !q || !dots) return fail(LB_ERR_ARG, "lb_scores: NULL pointer");
+    if (n < 1 || n > N) return fail(LB_ERR_ARG, "lb_scores: n=%d outside [1, N=%d]", n, N);
+    if (!aligned16(V) || !aligned16(q)) return fail(LB_ERR_ALIGN, "lb_scores: V and q must be 16-byte aligned");
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    cudaError_t e = lb::launch_scores(dtype, V, q, dots, n_tok, d, n, di.sms, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_scores launch");
+}
+
+int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const void *base, const float *cbar,
+                const float *c0, void *out, float *TC, float *LG, float *LSE, float *LSE0, int64_t n_tok, int d, int N,
+                int n, int dtype, void *stream) {
+    int rc = check_common(n_tok, d, dtype);
+    if (rc) return rc;
+    if (!V || !R || !DOTS || !base || !cbar || !c0 || !out || !TC) return fail(LB_ERR_ARG, "lb_read_fwd: NULL pointer");
+    if ((LG != nullptr) != (LSE != nullptr) || (LG != nullptr) != (LSE0 != nullptr))
+        return fail(LB_ERR_ARG, "lb_read_fwd: LG, LSE and LSE0 must be given together");
+    if (n < 1 || n > N) return fail(LB_ERR_ARG, "lb_read_fwd: n=%d outside [1, N=%d]", n, N);
+    if (n > LB_MAX_SOURCES) return fail(LB_ERR_UNSUPPORTED, "lb_read_fwd: n=%d exceeds LB_MAX_SOURCES=%d", n, LB_MAX_SOURCES);
+    if (qi < 0) return fail(LB_ERR_ARG, "lb_read_fwd: query row %d is negative", qi);
+    if (!aligned16(V) || !aligned16(base) || !aligned16(out))
+        return fail(LB_ERR_ALIGN, "lb_read_fwd: V, base and out must be 16-byte aligned");
+    if (n_tok == 0) return LB_OK;
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+
+    const int nch = chunks_of(d, dtype);
+    const long long tok_tiles = (n_tok + 7) / 8;
+    // fragments per warp: the widest tile that wastes no shared memory, narrowed until the grid fills the GPU
+    int fr = g_opt.fwd_fr;
+    if (fr < 1 || fr > 4) {
+        int best = 1, best_waste = 1 << 30;
+        for (int f = 4; f >= 1; --f) {
+            const int cg = (nch + f - 1) / f;
+            const int waste = cg * f - nch;
+            if (waste < best_waste) { best_waste = waste; best = f; }
+        }
+        fr = best;
+        while (fr > 1 && tok_tiles * ((nch + fr - 1) / fr) < di.sms) --fr;
+    }
+    const int cg = (nch + fr - 1) / fr;
+    int stages = g_opt.fwd_stages > 0 ? g_opt.fwd_stages : 8;
+    if (stages > 12) stages = 12;
+    while (stages > 2 && lb::read_fwd_smem_bytes(fr, stages) > kMaxSmem) --stages;
+
+    CUtensorMap tmV, tmB;
+    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, 8))) return rc;
+    if ((rc = make_map(&tmB, base, dtype, n_tok, d, 0, 8))) return rc;
+
+    lb::ReadFwdParams p;
+    p.R = R;
+    p.dots = DOTS + (long long)qi * N * n_tok;
+    p.cbar = cbar; p.c0 = c0; p.out = out; p.TC = TC; p.LG = LG; p.LSE = LSE; p.LSE0 = LSE0;
+    p.n_tok = n_tok; p.d = d; p.n = n; p.chunks = nch; p.col_groups = cg; p.tok_tiles = tok_tiles;
+    p.stages = stages;
+    p.inv_sqrt_d = 1.0f / sqrtf((float)d);
+    p.err_word = di.err_word;
+    const long long tiles = tok_tiles * cg;
+    int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
+    if (cap > kMaxGrid) cap = kMaxGrid;
+    const int grid = (int)(tiles < cap ? tiles : cap);
+    cudaError_t e = lb::launch_read_fwd(dtype, fr, tmV, tmB, p, grid, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_read_fwd launch");
+}
+
+size_t lb_read_bwd_scratch_bytes(int d) { return d > 0 ? (size_t)kMaxGrid * (size_t)d * sizeof(float) : 0; }
+
+int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
+                const float *cbar, const float *c0, const float *LG, const float *LSE, const float *LSE0, float *dcbar,
+                float *dq, void *scratch, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream) {
+    int rc = check_common(n_tok, d, dtype);
+    if (rc) return rc;
+    if (!V || !R || !dV || !dR || !q || !g || !cbar || !c0 || !LG || !LSE || !LSE0 || !dcbar || !dq || !scratch)
+        return fail(LB_ERR_ARG, "lb_read_bwd: NULL pointer");
+    if (n < 1 || n > N) return fail(LB_ERR_ARG, "lb_read_bwd: n=%d outside [1, N=%d]", n, N);
+    if (n > LB_MAX_SOURCES) return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: n=%d exceeds LB_MAX_SOURCES=%d", n, LB_MAX_SOURCES);
+    if (!aligned16(V) || !aligned16(dV) || !aligned16(g) || !aligned16(q) || !aligned16(scratch))
+        return fail(LB_ERR_ALIGN, "lb_read_bwd: V, dV, g, q and scratch must be 16-byte aligned");
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (n_tok == 0) {
+        cudaError_t e0 = cudaMemsetAsync(dq, 0, sizeof(float) * d, st);
+        return e0 == cudaSuccess ? LB_OK : cuda_fail(e0, "cudaMemsetAsync(dq)");
+    }
+
+    const int nch = chunks_of(d, dtype);
+    int wpt = 1;
+    while (wpt < 8 && (nch + wpt - 1) / wpt > 4) wpt <<= 1;
+    const int fr = (nch + wpt - 1) / wpt;
+    if (fr > 4) return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: d=%d needs more than 32 chunks per row", d);
+    const int bt = 8 / wpt;
+    const int vec = dtype == LB_DTYPE_BF16 ? 8 : 4;
+    int stages = g_opt.bwd_stages > 0 ? g_opt.bwd_stages : 8;
+    if (stages > 12) stages = 12;
+    while (stages > 2 && lb::read_bwd_smem_bytes(fr, wpt, stages, n, vec) > kMaxSmem) --stages;
+    if (lb::read_bwd_smem_bytes(fr, wpt, stages, n, vec) > kMaxSmem)
+        return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: shared memory does not fit for d=%d, n=%d", d, n);
+
+    CUtensorMap tmV, tmG, tmDV;
+    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, bt))) return rc;
+    if ((rc = make_map(&tmG, g, dtype, n_tok, d, 0, bt))) return rc;
+    if ((rc = make_map(&tmDV, dV, dtype, n_tok, d, N, bt))) return rc;
+
+    lb::ReadBwdParams p;
+    p.R = R; p.dR = dR; p.dV = dV; p.q = q; p.gt = gt; p.cbar = cbar; p.c0 = c0; p.LSE = LSE; p.LSE0 = LSE0; p.LG = LG;
+    p.dcbar = dcbar; p.dq_part = static_cast<float *>(scratch);
+    p.n_tok = n_tok; p.tok_tiles = (n_tok + bt - 1) / bt; p.d = d; p.n = n; p.chunks = nch; p.wpt = wpt;
+    p.stages = stages; p.accum = accum ? 1 : 0; p.inv_sqrt_d = 1.0f / sqrtf((float)d);
+    p.err_word = di.err_word;
+    int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
+    if (cap > kMaxGrid) cap = kMaxGrid;
+    const int grid = (int)(p.tok_tiles < cap ? p.tok_tiles : cap);
+    cudaError_t e = lb::launch_read_bwd(dtype, fr, tmV, tmG, tmDV, p, grid, st);
+    if (e != cudaSuccess) return cuda_fail(e, "lb_read_bwd launch");
+    e = lb::launch_dq_reduce(p.dq_part, grid, dq, d, p.inv_sqrt_d, st);
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_read_bwd dq reduction launch");
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

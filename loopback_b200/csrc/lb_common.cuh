@@ -1,0 +1,253 @@
+// Shared device/host helpers of the Loopback read kernels (sm_100a).
+//
+// Data model used by every kernel in this directory
+//   * a "row" is one token's d elements; rows are cut into CHUNKS of 512 bytes (256 bf16 / 128 fp32 columns);
+//   * a FRAGMENT is 16 bytes of a chunk (8 bf16 / 4 fp32); lane l of a warp owns fragment l of a chunk, so one
+//     warp instruction touches one whole 512-byte chunk row (conflict-free in shared memory, coalesced in HBM);
+//   * streaming kernels stage TILES of BT tokens x NCHT chunks in shared memory with TMA
+//     (cp.async.bulk.tensor, no multicast), laid out [chunk][token][512 B].
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lb {
+
+constexpr int kChunkBytes = 512;          // one TMA box row
+constexpr int kMaxSources = 128;          // n (= sources of a read) the shared-memory scalar tables are sized for
+constexpr int kConsumerWarps = 8;
+
+// ---------------------------------------------------------------------------------------------------------
+// device-side error word: kernels never trap or spin forever; a wait that runs out records where and returns.
+// ---------------------------------------------------------------------------------------------------------
+enum DeviceError : int {
+    kDevOk = 0,
+    kDevWaitFull = 1,      // a consumer gave up waiting for a TMA tile
+    kDevWaitEmpty = 2,     // the producer gave up waiting for a free stage
+    kDevWaitScalars = 3,   // a consumer gave up waiting for the scalar tables of a tile
+    kDevWaitScalarSlot = 4,
+    kDevWaitDrain = 5,     // the producer gave up waiting for its own copies in flight at exit
+};
+
+// The error word itself is a __device__ int owned by lb_api.cu (one per device); kernels get its address.
+
+// ---------------------------------------------------------------------------------------------------------
+// PTX wrappers: mbarrier + TMA
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. `abort_flag` lives in shared memory: the first wait of a CTA that runs out sets it (and the
+// device error word), every later wait of that CTA then fails at once, so a stuck CTA unwinds in one time-out.
+constexpr long long kWaitCycles = 4000000000LL;   // ~2 s at B200 clocks
+
+struct WaitCtx {
+    volatile int *abort_flag;   // shared memory, per CTA
+    int *err_word;              // global memory, per device
+};
+
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const WaitCtx &wc, int what) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 255u) == 0u) {
+            if (*wc.abort_flag) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                *wc.abort_flag = what;
+                atomicCAS(wc.err_word, 0, what);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// storage types: a fragment is one uint4 (16 B) holding VEC elements
+// ---------------------------------------------------------------------------------------------------------
+template <typename T> struct Store;
+
+template <> struct Store<__nv_bfloat16> {
+    static constexpr int kVec = 8;
+    static constexpr int kBytes = 2;
+    static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    // bf16 -> fp32 is a shift: exact
+    __device__ __forceinline__ static void unpack(const uint4 &u, float (&f)[8]) {
+        f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+        f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+        f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+        f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+    }
+    __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);      // round-to-nearest-even, .x = lo
+        return *reinterpret_cast<uint32_t *>(&b);
+    }
+    __device__ __forceinline__ static uint4 pack(const float (&f)[8]) {
+        return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+    }
+    // the value a store of `x` would hold, back in fp32
+    __device__ __forceinline__ static float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+};
+
+template <> struct Store<float> {
+    static constexpr int kVec = 4;
+    static constexpr int kBytes = 4;
+    static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    __device__ __forceinline__ static void unpack(const uint4 &u, float (&f)[4]) {
+        f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y);
+        f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+    }
+    __device__ __forceinline__ static uint4 pack(const float (&f)[4]) {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                          __float_as_uint(f[3]));
+    }
+    __device__ __forceinline__ static float round(float x) { return x; }
+};
+
+__device__ __forceinline__ uint4 ld_shared_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(smem_u32(p)));
+    return v;
+}
+
+// streaming global accesses: read-once data bypasses L1, stores do not allocate in L1
+__device__ __forceinline__ uint4 ld_global_stream_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_global_v4(void *p, const uint4 &v) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// reductions inside aligned groups of `width` lanes (width a power of two <= 32)
+__device__ __forceinline__ float group_sum(float v, int width) {
+    for (int o = width >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float group_max(float v, int width) {
+    for (int o = width >> 1; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// the per-read prior tables every kernel derives from c0 (n floats in device memory):
+//   lc_i = log(max(c0_i, 1e-8)), mass = sum_i c0_i, lse0 = logsumexp(lc), p0_i = exp(lc_i - lse0)
+// computed by one warp with the SAME instruction sequence that the scored softmax uses, so that a zero query
+// gives p == p0 bit for bit.
+// ---------------------------------------------------------------------------------------------------------
+struct PriorTables {
+    float c0[kMaxSources];
+    float lc[kMaxSources];
+    float p0[kMaxSources];
+    float mass;
+    float lse0;
+};
+
+// log-sum-exp over the n values held as x[k] for source i = lane + 32 k; every lane returns the result
+__device__ __forceinline__ float warp_lse(const float (&x)[kMaxSources / 32], int n, int lane) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < kMaxSources / 32; ++k)
+        if (lane + 32 * k < n) mx = fmaxf(mx, x[k]);
+    mx = group_max(mx, 32);
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxSources / 32; ++k)
+        if (lane + 32 * k < n) s += expf(x[k] - mx);
+    s = group_sum(s, 32);
+    return mx + logf(s);
+}
+
+__device__ __forceinline__ void build_prior_tables(PriorTables *pt, const float *__restrict__ c0, int n, int lane) {
+    float lc[kMaxSources / 32], c[kMaxSources / 32];
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxSources / 32; ++k) {
+        int i = lane + 32 * k;
+        c[k] = i < n ? c0[i] : 0.f;
+        lc[k] = logf(fmaxf(c[k], 1e-8f));
+        m += c[k];
+    }
+    m = group_sum(m, 32);
+    float lse0 = warp_lse(lc, n, lane);
+#pragma unroll
+    for (int k = 0; k < kMaxSources / 32; ++k) {
+        int i = lane + 32 * k;
+        if (i < n) {
+            pt->c0[i] = c[k];
+            pt->lc[i] = lc[k];
+            pt->p0[i] = expf(lc[k] - lse0);
+        }
+    }
+    if (lane == 0) { pt->mass = m; pt->lse0 = lse0; }
+}
+
+}  // namespace lb

@@ -1,0 +1,94 @@
+// Internal interface between the C-ABI layer (lb_api.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#define LB_DTYPE_F32 0
+#define LB_DTYPE_BF16 1
+
+namespace lb {
+
+struct ReadFwdParams {
+    const float *R;        // [N][n_tok] key scales
+    const float *dots;     // [N][n_tok] the scores of this read's query (row block of DOTS, or a scratch row block)
+    const float *cbar;     // [n_tok][n] installed coefficients
+    const float *c0;       // [n] the read's prior
+    void *out;             // [n_tok][d]
+    float *TC;             // [n_tok][n]
+    float *LG;             // [n_tok][n] logits, or null (no backward)
+    float *LSE;            // [n_tok] or null
+    float *LSE0;           // [n_tok] or null
+    long long n_tok;
+    int d;
+    int n;
+    int chunks;            // ceil(d * elem / 512)
+    int col_groups;        // ceil(chunks / FR)
+    long long tok_tiles;   // ceil(n_tok / 8)
+    int stages;
+    float inv_sqrt_d;
+    int *err_word;         // device error word (see lb_device_error)
+};
+
+size_t read_fwd_smem_bytes(int fr, int stages);
+cudaError_t launch_read_fwd(int dtype, int fr, const CUtensorMap &tmV, const CUtensorMap &tmBase,
+                            const ReadFwdParams &p, int grid, cudaStream_t stream);
+cudaError_t launch_scores(int dtype, const void *V, const float *q, float *dots, long long n_tok, int d, int n,
+                          int sms, cudaStream_t stream);
+
+struct WriteParams {
+    const void *h;         // [n_tok][d]
+    const void *x;         // [n_tok][d]
+    void *v;               // [n_tok][d]  (slice s of the stack)
+    float *r;              // [n_tok]     (slice s of R), may be null
+    const float *Q;        // [NQ][d] fp32 queries, or null (no scores)
+    float *dots_s;         // DOTS + s * n_tok: element (j, t) at dots_s[j * N * n_tok + t]
+    long long n_tok;
+    long long dots_qstride;   // N * n_tok
+    int d;
+    int j0;                // first query whose read sees this update
+    int nq;                // queries j0 .. j0 + nq - 1 are scored
+    float eps;
+};
+
+cudaError_t launch_write(int dtype, const WriteParams &p, int sms, cudaStream_t stream);
+cudaError_t launch_rstd_fwd(int dtype, const void *x, float *r, long long n_tok, int d, float eps, int sms,
+                            cudaStream_t stream);
+// mode 0: gx = gr (-r^3/d) x written;  mode 1: gx += round(gr (-r^3/d) x), rounded to the storage type
+cudaError_t launch_rstd_bwd(int dtype, const void *x, const float *r, const float *gr, void *gx, long long n_tok,
+                            int d, int mode, int sms, cudaStream_t stream);
+cudaError_t launch_neg(int dtype, const void *g, void *out, long long n_elem, int sms, cudaStream_t stream);
+
+struct ReadBwdParams {
+    const float *R;        // [N][n_tok]
+    float *dR;             // [N][n_tok]
+    void *dV;              // [N][n_tok][d] (stores go here; loads of the old value come through TMA)
+    const float *q;        // [d] fp32
+    const float *gt;       // [n_tok][n] or null
+    const float *cbar;     // [n_tok][n]
+    const float *c0;       // [n]
+    const float *LSE;      // [n_tok]
+    const float *LSE0;     // [n_tok]
+    const float *LG;       // [n_tok][n]
+    float *dcbar;          // [n_tok][n]
+    float *dq_part;        // [grid][d] scratch: one partial row per CTA
+    long long n_tok;
+    long long tok_tiles;
+    int d;
+    int n;
+    int chunks;
+    int wpt;               // warps per token (1, 2, 4 or 8); tokens per tile = 8 / wpt
+    int stages;
+    int accum;             // 0: dV / dR are written; 1: added into
+    float inv_sqrt_d;
+    int *err_word;
+};
+
+size_t read_bwd_smem_bytes(int fr, int wpt, int stages, int n, int vec);
+cudaError_t launch_read_bwd(int dtype, int fr, const CUtensorMap &tmV, const CUtensorMap &tmG,
+                            const CUtensorMap &tmDV, const ReadBwdParams &p, int grid, cudaStream_t stream);
+cudaError_t launch_dq_reduce(const float *dq_part, int rows, float *dq, int d, float scale, cudaStream_t stream);
+
+}  // namespace lb

@@ -1,0 +1,420 @@
+// Backward of one read over the stacked updates (sm_100a): one kernel, one pass over V, one pass over dV.
+//
+// Given g = dL/dout [n_tok, d] and gt = dL/dtc [n_tok, n] (optional), with p_i = exp(LG_i - LSE) saved by the forward:
+//   phase 1 (streams V[i] once):   gd_i = g . v_i     gp_i = mass (gd_i + gt_i)     S = sum_i p_i gp_i
+//                                  A = sum_i p_i r_i gp_i v_i      B = sum_i p_i r_i v_i
+//                                  dq partial += A - S B                       (scaled by 1/sqrt(d) at the end)
+//   scalars:                       dz_i = p_i (gp_i - S)    dR[i] (+)= dz_i (LG_i - lc_i) / r_i    dcbar_i = -gd_i
+//   phase 2 (streams dV[i] once):  dV[i] (+)= w_i g + dz_i r_i q / sqrt(d),   w_i = c0_i - cbar_i + mass (p_i - p0_i)
+// In accumulate mode the old dV / dR are read and the sum is rounded to the storage type after the new term was
+// rounded on its own (bf16: exactly what a bf16 autograd add_ of a bf16 gradient does).
+//
+// Replaces the reference's two backward kernels and the torch reduction between them (fused_dattn.py:459-536,
+// :761-793): no GD / SACC round trip through HBM, g is read once, and the query gradient leaves the kernel as one
+// partial row per CTA.
+//
+// Tiles are (8 / WPT) tokens x the full row; a token's row is split over WPT consumer warps (FR chunks of 512 B
+// each). Warp roles as in the forward read: 8 consumer warps, 1 TMA producer lane, 2 scalar warps that prepare the
+// per-(token, source) tables of the next tile. All waits are bounded.
+#include "lb_common.cuh"
+#include "lb_kernels.h"
+
+namespace lb {
+
+constexpr int kBwdScalarWarps = 2;
+constexpr int kBwdThreads = (kConsumerWarps + 1 + kBwdScalarWarps) * 32;
+constexpr int kBwdMaxStages = 12;
+constexpr int kBwdTables = 6;     // P, R, GT, W, ZL, DRP
+
+struct BwdSmemTail {
+    float c0[kMaxSources];
+    float lc[kMaxSources];
+    float mass;
+    int abort_flag;
+    float xch[2][kConsumerWarps];               // partial g.v of the token's warps, double buffered by source
+    uint64_t full[kBwdMaxStages];
+    uint64_t empty[kBwdMaxStages];
+    uint64_t sfull[2];
+    uint64_t sempty[2];
+};
+
+// dynamic shared memory: [stages][tables 2 x 6 x n_pad*BT][gdkq n_pad*BT][dq slots][tail]
+__host__ __device__ inline int bwd_npad(int n) { return (n + 3) & ~3; }
+__host__ __device__ inline size_t bwd_table_floats(int n, int wpt) { return (size_t)bwd_npad(n) * (kConsumerWarps / wpt); }
+
+size_t read_bwd_smem_bytes(int fr, int wpt, int stages, int n, int vec) {
+    size_t stage = (size_t)fr * kConsumerWarps * kChunkBytes;
+    size_t tables = (2 * kBwdTables + 1) * bwd_table_floats(n, wpt) * sizeof(float);
+    size_t slots = (size_t)fr * vec * sizeof(float) * kConsumerWarps * 32;
+    return 1024 + stages * stage + ((tables + 15) & ~size_t(15)) + slots + sizeof(BwdSmemTail) + 64;
+}
+
+template <typename T, int FR>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
+                const __grid_constant__ CUtensorMap tmDV, ReadBwdParams p) {
+    using S = Store<T>;
+    constexpr int VEC = S::kVec;
+    constexpr int V4 = VEC / 4;
+    constexpr int BW = kChunkBytes / S::kBytes;
+    constexpr int kStageBytes = FR * kConsumerWarps * kChunkBytes;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NS = p.stages, n = p.n, WPT = p.wpt, BT = kConsumerWarps / WPT;
+    const size_t tfl = bwd_table_floats(n, WPT);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float *tables = reinterpret_cast<float *>(stages + (size_t)NS * kStageBytes);
+    float *gdkq = tables + 2 * kBwdTables * tfl;
+    float4 *slots = reinterpret_cast<float4 *>(
+        (reinterpret_cast<uintptr_t>(gdkq + tfl) + 15) & ~uintptr_t(15));
+    BwdSmemTail *sm = reinterpret_cast<BwdSmemTail *>(
+        (reinterpret_cast<uintptr_t>(slots + (size_t)FR * V4 * kConsumerWarps * 32) + 15) & ~uintptr_t(15));
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], kConsumerWarps); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm->sfull[b], kBwdScalarWarps); mbar_init(&sm->sempty[b], kConsumerWarps); }
+        sm->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == kConsumerWarps + 1) {
+        float m = 0.f;
+        for (int i = lane; i < kMaxSources; i += 32) {
+            float c = i < n ? p.c0[i] : 0.f;
+            if (i < n) { sm->c0[i] = c; sm->lc[i] = logf(fmaxf(c, 1e-8f)); }
+            m += c;
+        }
+        m = group_sum(m, 32);
+        if (lane == 0) sm->mass = m;
+    }
+    if (warp < kConsumerWarps) {
+#pragma unroll
+        for (int k = 0; k < FR * V4; ++k) slots[(size_t)k * kConsumerWarps * 32 + threadIdx.x] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __syncthreads();
+    const WaitCtx wc{&sm->abort_flag, p.err_word};
+    const long long n_tiles = p.tok_tiles;
+    const int items_per_tile = 1 + n + (p.accum ? n : 0);
+
+    if (warp < kConsumerWarps) {
+        // ------------------------------------------------------------------ consumers
+        const int t = warp / WPT;                 // token of the tile
+        const int part = warp - t * WPT;          // which slice of the row
+        const int chunk0 = part * FR;
+        const int row0 = chunk0 * BT + t;         // stage row of fragment k: row0 + k * BT
+        const float mass = sm->mass, inv = p.inv_sqrt_d;
+        const int bar_id = 1 + t, bar_threads = WPT * 32;
+        long long it = 0;
+        int tcount = 0;
+        // A wait that runs out must not make this warp leave: its sibling warps meet it at named barriers. It
+        // turns `alive` off instead, and the warp walks the remaining (finite) loop structure without waiting or
+        // storing, so every barrier still gets all its arrivals.
+        bool alive = true;
+        bool valid[FR];
+#pragma unroll
+        for (int k = 0; k < FR; ++k) valid[k] = chunk0 + k < p.chunks;
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+        for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+            const long long tok = tile * BT + t;
+            const bool tok_in = tok < p.n_tok;
+            const int buf = tcount & 1;
+            const float *tb = tables + (size_t)buf * kBwdTables * tfl;
+            const float *tP = tb, *tR = tb + tfl, *tGT = tb + 2 * tfl, *tW = tb + 3 * tfl, *tZL = tb + 4 * tfl,
+                        *tDRP = tb + 5 * tfl;
+            // ---- g tile -> registers
+            uint4 gu[FR];
+            {
+                const int st = (int)(it % NS);
+                if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                const uint8_t *sb = stages + (size_t)st * kStageBytes;
+#pragma unroll
+                for (int k = 0; k < FR; ++k) gu[k] = valid[k] ? ld_shared_v4(sb + ((size_t)(row0 + k * BT) * 32 + lane) * 16) : zero4;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->empty[st]);
+                ++it;
+            }
+            if (alive && !mbar_wait(&sm->sfull[buf], (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
+
+            // ---- phase 1: one pass over the sources, the accumulation of source i-1 overlapping the dot of i
+            float A[FR][VEC], B[FR][VEC];
+#pragma unroll
+            for (int k = 0; k < FR; ++k)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) { A[k][e] = 0.f; B[k][e] = 0.f; }
+            float sacc = 0.f, dot_prev = 0.f;
+            uint4 vprev[FR];
+#pragma unroll
+            for (int k = 0; k < FR; ++k) vprev[k] = make_uint4(0, 0, 0, 0);
+            for (int i = 0; i <= n; ++i) {
+                uint4 vcur[FR];
+                float dot = 0.f;
+                if (i < n) {
+                    const int st = (int)(it % NS);
+                    if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                    const uint8_t *sb = stages + (size_t)st * kStageBytes;
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) vcur[k] = valid[k] ? ld_shared_v4(sb + ((size_t)(row0 + k * BT) * 32 + lane) * 16) : zero4;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm->empty[st]);
+                    ++it;
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) {
+                        float gf[VEC], vf[VEC];
+                        S::unpack(gu[k], gf);
+                        S::unpack(vcur[k], vf);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) dot = fmaf(gf[e], vf[e], dot);
+                    }
+                    dot = warp_sum(dot);
+                    if (WPT > 1 && lane == 0) sm->xch[i & 1][warp] = dot;
+                } else {
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) vcur[k] = make_uint4(0, 0, 0, 0);
+                }
+                if (i > 0) {
+                    const int j = i - 1;
+                    float gd = dot_prev;
+                    if (WPT > 1) {
+                        gd = 0.f;
+                        for (int w2 = 0; w2 < WPT; ++w2) gd += sm->xch[j & 1][t * WPT + w2];
+                    }
+                    if (part == 0 && lane == 0) gdkq[j * BT + t] = gd;
+                    const float pj = tP[j * BT + t], rj = tR[j * BT + t];
+                    const float gp = mass * (gd + tGT[j * BT + t]);
+                    sacc = fmaf(pj, gp, sacc);
+                    const float b = pj * rj, a = b * gp;
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) {
+                        float vf[VEC];
+                        S::unpack(vprev[k], vf);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) { A[k][e] = fmaf(a, vf[e], A[k][e]); B[k][e] = fmaf(b, vf[e], B[k][e]); }
+                    }
+                }
+                if (WPT > 1) named_bar_sync(bar_id, bar_threads);
+                dot_prev = dot;
+#pragma unroll
+                for (int k = 0; k < FR; ++k) vprev[k] = vcur[k];
+            }
+            // ---- query-gradient partial of this thread's columns: private shared-memory slots
+#pragma unroll
+            for (int k = 0; k < FR; ++k)
+#pragma unroll
+                for (int e4 = 0; e4 < V4; ++e4) {
+                    float4 *sp = &slots[(size_t)(k * V4 + e4) * kConsumerWarps * 32 + threadIdx.x];
+                    float4 s4 = *sp;
+                    if (alive && tok_in) {
+                        s4.x += A[k][4 * e4 + 0] - sacc * B[k][4 * e4 + 0];
+                        s4.y += A[k][4 * e4 + 1] - sacc * B[k][4 * e4 + 1];
+                        s4.z += A[k][4 * e4 + 2] - sacc * B[k][4 * e4 + 2];
+                        s4.w += A[k][4 * e4 + 3] - sacc * B[k][4 * e4 + 3];
+                    }
+                    *sp = s4;
+                }
+            // ---- per-source scalars of this token: lanes over sources, by the token's first warp
+            __syncwarp();
+            if (part == 0) {
+                for (int i = lane; i < n; i += 32) {
+                    const float gd = gdkq[i * BT + t];
+                    const float pi = tP[i * BT + t], ri = tR[i * BT + t];
+                    const float gp = mass * (gd + tGT[i * BT + t]);
+                    const float dz = pi * (gp - sacc);
+                    gdkq[i * BT + t] = dz * ri * inv;
+                    if (alive && tok_in) {
+                        p.dR[(long long)i * p.n_tok + tok] = tDRP[i * BT + t] + dz * tZL[i * BT + t];
+                        p.dcbar[tok * n + i] = -gd;
+                    }
+                }
+            }
+            if (WPT > 1) named_bar_sync(bar_id, bar_threads); else __syncwarp();
+
+            // ---- phase 2: the gradient of every source
+            float qf[FR][VEC];
+#pragma unroll
+            for (int k = 0; k < FR; ++k) {
+                const int col = (chunk0 + k) * BW + lane * VEC;
+#pragma unroll
+                for (int e4 = 0; e4 < V4; ++e4) {
+                    float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (col < p.d) q4 = __ldg(reinterpret_cast<const float4 *>(p.q + col) + e4);
+                    qf[k][4 * e4] = q4.x; qf[k][4 * e4 + 1] = q4.y; qf[k][4 * e4 + 2] = q4.z; qf[k][4 * e4 + 3] = q4.w;
+                }
+            }
+            T *dvbase = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d;
+            const long long src_stride = p.n_tok * (long long)p.d;
+            for (int i = 0; i < n; ++i) {
+                const float wi = tW[i * BT + t], kq = gdkq[i * BT + t];
+                uint4 prev[FR];
+                if (p.accum) {
+                    const int st = (int)(it % NS);
+                    if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                    const uint8_t *sb = stages + (size_t)st * kStageBytes;
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? ld_shared_v4(sb + ((size_t)(row0 + k * BT) * 32 + lane) * 16) : zero4;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm->empty[st]);
+                    ++it;
+                }
+#pragma unroll
+                for (int k = 0; k < FR; ++k) {
+                    float gf[VEC], o[VEC];
+                    S::unpack(gu[k], gf);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) o[e] = fmaf(wi, gf[e], kq * qf[k][e]);
+                    if (p.accum) {
+                        float pf[VEC];
+                        S::unpack(prev[k], pf);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) o[e] = pf[e] + S::round(o[e]);
+                    }
+                    const int col = (chunk0 + k) * BW + lane * VEC;
+                    if (alive && tok_in && col < p.d) st_global_v4(dvbase + (long long)i * src_stride + col, S::pack(o));
+                }
+            }
+            // the token's warps leave the tile together: gdkq and xch are reused by the next tile
+            if (WPT > 1) named_bar_sync(bar_id, bar_threads); else __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->sempty[buf]);
+        }
+        // ---- the CTA's query-gradient row: sum the private slots over the tile's tokens
+        named_bar_sync(15, kConsumerWarps * 32);
+        if (t == 0) {
+#pragma unroll
+            for (int k = 0; k < FR; ++k) {
+                const int col = (chunk0 + k) * BW + lane * VEC;
+#pragma unroll
+                for (int e4 = 0; e4 < V4; ++e4) {
+                    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int t2 = 0; t2 < BT; ++t2) {
+                        const float4 v4 = slots[(size_t)(k * V4 + e4) * kConsumerWarps * 32 + (t2 * WPT + part) * 32 + lane];
+                        s4.x += v4.x; s4.y += v4.y; s4.z += v4.z; s4.w += v4.w;
+                    }
+                    if (col < p.d)
+                        *reinterpret_cast<float4 *>(p.dq_part + (long long)blockIdx.x * p.d + col + 4 * e4) = s4;
+                }
+            }
+        }
+    } else if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmV);
+            tma_prefetch_desc(&tmG);
+            if (p.accum) tma_prefetch_desc(&tmDV);
+            long long it = 0;
+            bool ok = true;
+            const int nch = p.chunks;                       // the full row
+            for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const int tok0 = (int)(tile * BT);
+                for (int item = 0; item < items_per_tile; ++item, ++it) {
+                    const int st = (int)(it % NS);
+                    if (!mbar_wait(&sm->empty[st], (uint32_t)(((it / NS) & 1) ^ 1), wc, kDevWaitEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *sb = stages + (size_t)st * kStageBytes;
+                    mbar_arrive_expect_tx(&sm->full[st], (uint32_t)(nch * BT * kChunkBytes));
+                    for (int c = 0; c < nch; ++c) {
+                        uint8_t *dst = sb + (size_t)c * BT * kChunkBytes;
+                        if (item == 0) tma_load_2d(dst, &tmG, &sm->full[st], c * BW, tok0);
+                        else if (item <= n) tma_load_3d(dst, &tmV, &sm->full[st], c * BW, tok0, item - 1);
+                        else tma_load_3d(dst, &tmDV, &sm->full[st], c * BW, tok0, item - 1 - n);
+                    }
+                }
+            }
+            if (!ok) {
+                const long long first = it > NS ? it - NS : 0;
+                long long t0 = clock64();
+                for (long long f = first; f < it; ++f) {
+                    const int st = (int)(f % NS);
+                    while (!mbar_try_wait(&sm->full[st], (uint32_t)((f / NS) & 1))) {
+                        if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ scalar warps: tables of the next tile
+        const int sw = warp - kConsumerWarps - 1;
+        const float mass = sm->mass;
+        int tcount = 0;
+        for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+            const int buf = tcount & 1;
+            if (!mbar_wait(&sm->sempty[buf], (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
+                return;
+            float *tb = tables + (size_t)buf * kBwdTables * tfl;
+            for (int idx = sw * 32 + lane; idx < BT * n; idx += kBwdScalarWarps * 32) {
+                const int t = idx / n, i = idx - t * n;
+                long long tok = tile * BT + t;
+                if (tok >= p.n_tok) tok = p.n_tok - 1;
+                const float lg = __ldg(p.LG + tok * n + i);
+                const float lse = __ldg(p.LSE + tok), lse0 = __ldg(p.LSE0 + tok);
+                const float cb = __ldg(p.cbar + tok * n + i);
+                const float gtv = p.gt ? __ldg(p.gt + tok * n + i) : 0.f;
+                const float r = __ldg(p.R + (long long)i * p.n_tok + tok);
+                const float drp = p.accum ? p.dR[(long long)i * p.n_tok + tok] : 0.f;
+                const float lci = sm->lc[i];
+                const float pi = expf(lg - lse), p0 = expf(lci - lse0);
+                const int o = i * BT + t;
+                tb[o] = pi;
+                tb[tfl + o] = r;
+                tb[2 * tfl + o] = gtv;
+                tb[3 * tfl + o] = sm->c0[i] - cb + mass * (pi - p0);
+                tb[4 * tfl + o] = (lg - lci) / r;
+                tb[5 * tfl + o] = drp;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->sfull[buf]);
+        }
+    }
+}
+
+template <typename T, int FR>
+static cudaError_t launch_bwd(const CUtensorMap &tmV, const CUtensorMap &tmG, const CUtensorMap &tmDV,
+                              const ReadBwdParams &p, int grid, cudaStream_t stream) {
+    size_t smem = read_bwd_smem_bytes(FR, p.wpt, p.stages, p.n, Store<T>::kVec);
+    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    read_bwd_kernel<T, FR><<<grid, kBwdThreads, smem, stream>>>(tmV, tmG, tmDV, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_read_bwd(int dtype, int fr, const CUtensorMap &tmV, const CUtensorMap &tmG,
+                            const CUtensorMap &tmDV, const ReadBwdParams &p, int grid, cudaStream_t stream) {
+#define LB_BWD_CASE(TT, F) return launch_bwd<TT, F>(tmV, tmG, tmDV, p, grid, stream)
+    if (dtype == LB_DTYPE_BF16) {
+        switch (fr) { case 1: LB_BWD_CASE(__nv_bfloat16, 1); case 2: LB_BWD_CASE(__nv_bfloat16, 2);
+                      case 3: LB_BWD_CASE(__nv_bfloat16, 3); case 4: LB_BWD_CASE(__nv_bfloat16, 4); }
+    } else {
+        switch (fr) { case 1: LB_BWD_CASE(float, 1); case 2: LB_BWD_CASE(float, 2);
+                      case 3: LB_BWD_CASE(float, 3); case 4: LB_BWD_CASE(float, 4); }
+    }
+#undef LB_BWD_CASE
+    return cudaErrorInvalidValue;
+}
+
+// dq[c] = scale * sum_rows dq_part[row][c]; fixed summation order (deterministic).
+// Replaces the torch reduction of the per-program partials (fused_dattn.py:785).
+__global__ void __launch_bounds__(256) dq_reduce_kernel(const float *__restrict__ part, int rows, float *__restrict__ dq,
+                                                        int d, float scale) {
+    __shared__ float red[8][33];
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int col = blockIdx.x * 32 + cx;
+    float s = 0.f;
+    if (col < d)
+        for (int r = ry; r < rows; r += 8) s += part[(long long)r * d + col];
+    red[ry][cx] = s;
+    __syncthreads();
+    if (ry == 0 && col < d) {
+        float tsum = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) tsum += red[k][cx];
+        dq[col] = tsum * scale;
+    }
+}
+
+cudaError_t launch_dq_reduce(const float *dq_part, int rows, float *dq, int d, float scale, cudaStream_t stream) {
+    dq_reduce_kernel<<<(d + 31) / 32, 256, 0, stream>>>(dq_part, rows, dq, d, scale);
+    return cudaGetLastError();
+}
+
+}  // namespace lb

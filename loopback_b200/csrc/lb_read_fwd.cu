@@ -1,0 +1,316 @@
+// Forward read from stored scores (sm_100a).
+//
+//   out[t, :] = base[t, :] + sum_{i<n} (tc[t,i] - cbar[t,i]) * V[i, t, :]
+//   tc[t,i]   = c0_i + mass * (softmax_i(dots[i,t] r[i,t] / sqrt(d) + lc_i) - softmax_i(lc_i))
+//
+// Replaces the reference's stored-score read kernel (fused_dattn.py:588-625) and the host preparation around it
+// (fused_dattn.py:735-745: log-prior and mass are formed in the kernel from c0).
+//
+// One persistent CTA per SM slot walks tiles of 8 tokens x FR chunks (a chunk is 512 B of a row). Warp roles:
+//   warps 0..7   consumers: warp w owns token w of the tile; lane l owns fragment l of each chunk; fp32 accumulators
+//   warp  8      producer: one lane issues TMA tile loads (base tile, then V[0..n) tiles) into a ring of stages
+//   warps 9..10  scalar warps: per tile, the n-source softmaxes of the 8 tokens -> coefficient table in shared
+//                memory (double buffered, one tile ahead of the consumers), and the saved TC / LG / LSE / LSE0
+// Every wait is bounded (see lb_common.cuh); nothing here spins forever or traps.
+#include "lb_common.cuh"
+#include "lb_kernels.h"
+
+namespace lb {
+
+constexpr int kFwdBT = 8;                         // tokens per tile == consumer warps
+constexpr int kFwdScalarWarps = 2;
+constexpr int kFwdThreads = (kConsumerWarps + 1 + kFwdScalarWarps) * 32;
+constexpr int kFwdMaxStages = 12;
+
+struct FwdSmemTail {
+    float wtab[2][kMaxSources * kFwdBT];          // coefficient deltas w[i][t], double buffered by tile
+    float c0[kMaxSources];
+    float lc[kMaxSources];
+    float mass;
+    int abort_flag;
+    uint64_t full[kFwdMaxStages];
+    uint64_t empty[kFwdMaxStages];
+    uint64_t sfull[2];
+    uint64_t sempty[2];
+};
+
+size_t read_fwd_smem_bytes(int fr, int stages) {
+    return 1024 + (size_t)stages * (size_t)fr * kFwdBT * kChunkBytes + sizeof(FwdSmemTail);
+}
+
+template <typename T, int FR>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBase, ReadFwdParams p) {
+    using S = Store<T>;
+    constexpr int VEC = S::kVec;
+    constexpr int BW = kChunkBytes / S::kBytes;               // columns per chunk
+    constexpr int kStageBytes = FR * kFwdBT * kChunkBytes;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    FwdSmemTail *sm = reinterpret_cast<FwdSmemTail *>(stages + (size_t)p.stages * kStageBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NS = p.stages;
+    const int n = p.n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], kConsumerWarps); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm->sfull[b], kFwdScalarWarps); mbar_init(&sm->sempty[b], kConsumerWarps); }
+        sm->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == kConsumerWarps + 1) {           // prior tables: c0, log-prior, mass
+        float m = 0.f;
+        for (int i = lane; i < kMaxSources; i += 32) {
+            float c = i < n ? p.c0[i] : 0.f;
+            if (i < n) { sm->c0[i] = c; sm->lc[i] = logf(fmaxf(c, 1e-8f)); }
+            m += c;
+        }
+        m = group_sum(m, 32);
+        if (lane == 0) sm->mass = m;
+    }
+    __syncthreads();
+    const WaitCtx wc{&sm->abort_flag, p.err_word};
+
+    const int cg_count = p.col_groups;
+    const long long n_tiles = (long long)p.tok_tiles * cg_count;
+
+    if (warp < kConsumerWarps) {
+        // ------------------------------------------------------------------ consumers
+        long long it = 0;
+        int tcount = 0;
+        bool alive = true;      // turned off by a wait that ran out: the warp then finishes its loops without waiting or storing
+        for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+            const long long tt = tile / cg_count;
+            const int cg = (int)(tile - tt * cg_count);
+            const long long tok = tt * kFwdBT + warp;
+            const int chunk0 = cg * FR;
+            const int buf = tcount & 1;
+            float acc[FR][VEC];
+            {   // item 0: the base tile
+                const int st = (int)(it % NS);
+                if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                const uint8_t *sb = stages + (size_t)st * kStageBytes;
+#pragma unroll
+                for (int k = 0; k < FR; ++k) {
+                    uint4 u = ld_shared_v4(sb + ((size_t)(k * kFwdBT + warp) * 32 + lane) * 16);
+                    S::unpack(u, acc[k]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->empty[st]);
+                ++it;
+            }
+            if (alive && !mbar_wait(&sm->sfull[buf], (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
+            const float *wt = sm->wtab[buf];
+            for (int i = 0; i < n; ++i, ++it) {
+                const int st = (int)(it % NS);
+                if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                const uint8_t *sb = stages + (size_t)st * kStageBytes;
+                const float wi = wt[i * kFwdBT + warp];
+                uint4 u[FR];
+#pragma unroll
+                for (int k = 0; k < FR; ++k) u[k] = ld_shared_v4(sb + ((size_t)(k * kFwdBT + warp) * 32 + lane) * 16);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->empty[st]);
+#pragma unroll
+                for (int k = 0; k < FR; ++k) {
+                    float v[VEC];
+                    S::unpack(u[k], v);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) acc[k][e] = fmaf(wi, v[e], acc[k][e]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->sempty[buf]);
+            if (alive && tok < p.n_tok) {
+                T *orow = reinterpret_cast<T *>(p.out) + tok * (long long)p.d;
+#pragma unroll
+                for (int k = 0; k < FR; ++k) {
+                    const int col = (chunk0 + k) * BW + lane * VEC;
+                    if (col < p.d) st_global_v4(orow + col, S::pack(acc[k]));
+                }
+            }
+        }
+    } else if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmV);
+            tma_prefetch_desc(&tmBase);
+            long long it = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const long long tt = tile / cg_count;
+                const int cg = (int)(tile - tt * cg_count);
+                const int tok0 = (int)(tt * kFwdBT);
+                const int chunk0 = cg * FR;
+                const int nch = min(FR, p.chunks - chunk0);
+                for (int item = -1; item < n; ++item, ++it) {
+                    const int st = (int)(it % NS);
+                    if (!mbar_wait(&sm->empty[st], (uint32_t)(((it / NS) & 1) ^ 1), wc, kDevWaitEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *sb = stages + (size_t)st * kStageBytes;
+                    mbar_arrive_expect_tx(&sm->full[st], (uint32_t)(nch * kFwdBT * kChunkBytes));
+                    for (int c = 0; c < nch; ++c) {
+                        if (item < 0)
+                            tma_load_2d(sb + (size_t)c * kFwdBT * kChunkBytes, &tmBase, &sm->full[st],
+                                        (chunk0 + c) * BW, tok0);
+                        else
+                            tma_load_3d(sb + (size_t)c * kFwdBT * kChunkBytes, &tmV, &sm->full[st],
+                                        (chunk0 + c) * BW, tok0, item);
+                    }
+                }
+            }
+            if (!ok) {
+                // unwinding: let the copies already issued land before the CTA's shared memory is released
+                const long long first = it > NS ? it - NS : 0;
+                long long t0 = clock64();
+                for (long long f = first; f < it; ++f) {
+                    const int st = (int)(f % NS);
+                    while (!mbar_try_wait(&sm->full[st], (uint32_t)((f / NS) & 1))) {
+                        if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ scalar warps
+        const int sw = warp - kConsumerWarps - 1;
+        const int G = n >= 32 ? 32 : (n <= 2 ? 2 : (n <= 4 ? 4 : (n <= 8 ? 8 : (n <= 16 ? 16 : 32))));
+        const int TPP = 32 / G;
+        const int sub = lane / G, ii = lane % G;
+        const float inv = p.inv_sqrt_d, mass = sm->mass;
+        int tcount = 0;
+        for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+            const long long tt = tile / cg_count;
+            const int cg = (int)(tile - tt * cg_count);
+            const int buf = tcount & 1;
+            if (!mbar_wait(&sm->sempty[buf], (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
+                return;
+            float *wt = sm->wtab[buf];
+            for (int pass = sw; pass * TPP < kFwdBT; pass += kFwdScalarWarps) {
+                const int t = pass * TPP + sub;
+                const long long tok_raw = tt * kFwdBT + t;
+                const bool tok_ok = tok_raw < p.n_tok;
+                const long long tok = tok_ok ? tok_raw : p.n_tok - 1;
+                float l[kMaxSources / 32], lcv[kMaxSources / 32], cb[kMaxSources / 32];
+#pragma unroll
+                for (int k = 0; k < kMaxSources / 32; ++k) {
+                    const int i = ii + 32 * k;
+                    const bool act = i < n && (k == 0 || G == 32);
+                    l[k] = -INFINITY; lcv[k] = -INFINITY; cb[k] = 0.f;
+                    if (act) {
+                        const float r = __ldg(p.R + (long long)i * p.n_tok + tok);
+                        const float dt = __ldg(p.dots + (long long)i * p.n_tok + tok);
+                        cb[k] = __ldg(p.cbar + tok * n + i);
+                        lcv[k] = sm->lc[i];
+                        l[k] = dt * r * inv + lcv[k];
+                    }
+                }
+                // the scored softmax and the prior-only softmax go through the same instructions on the same
+                // lanes: with a zero query (l == lc) they agree bit for bit, so tc == c0 and out == base exactly
+                float mx = l[0], mx0 = lcv[0];
+#pragma unroll
+                for (int k = 1; k < kMaxSources / 32; ++k) { mx = fmaxf(mx, l[k]); mx0 = fmaxf(mx0, lcv[k]); }
+                mx = group_max(mx, G); mx0 = group_max(mx0, G);
+                float s = 0.f, s0 = 0.f;
+#pragma unroll
+                for (int k = 0; k < kMaxSources / 32; ++k) {
+                    const int i = ii + 32 * k;
+                    const bool act = i < n && (k == 0 || G == 32);
+                    s += act ? expf(l[k] - mx) : 0.f;
+                    s0 += act ? expf(lcv[k] - mx0) : 0.f;
+                }
+                s = group_sum(s, G); s0 = group_sum(s0, G);
+                const float lse = mx + logf(s), lse0 = mx0 + logf(s0);
+#pragma unroll
+                for (int k = 0; k < kMaxSources / 32; ++k) {
+                    const int i = ii + 32 * k;
+                    const bool act = i < n && (k == 0 || G == 32);
+                    if (act) {
+                        const float pi = expf(l[k] - lse), p0 = expf(lcv[k] - lse0);
+                        const float tc = sm->c0[i] + mass * (pi - p0);
+                        wt[i * kFwdBT + t] = tc - cb[k];
+                        if (cg == 0 && tok_ok) {
+                            p.TC[tok * n + i] = tc;
+                            if (p.LG) p.LG[tok * n + i] = l[k];
+                        }
+                    }
+                }
+                if (ii == 0 && cg == 0 && tok_ok && p.LSE) { p.LSE[tok] = lse; p.LSE0[tok] = lse0; }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->sfull[buf]);
+        }
+    }
+}
+
+template <typename T, int FR>
+static cudaError_t launch_fwd(const CUtensorMap &tmV, const CUtensorMap &tmBase, const ReadFwdParams &p, int grid,
+                              cudaStream_t stream) {
+    size_t smem = read_fwd_smem_bytes(FR, p.stages);
+    cudaError_t e = cudaFuncSetAttribute(read_fwd_kernel<T, FR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    read_fwd_kernel<T, FR><<<grid, kFwdThreads, smem, stream>>>(tmV, tmBase, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_read_fwd(int dtype, int fr, const CUtensorMap &tmV, const CUtensorMap &tmBase,
+                            const ReadFwdParams &p, int grid, cudaStream_t stream) {
+#define LB_FWD_CASE(TT, F) return launch_fwd<TT, F>(tmV, tmBase, p, grid, stream)
+    if (dtype == LB_DTYPE_BF16) {
+        switch (fr) { case 1: LB_FWD_CASE(__nv_bfloat16, 1); case 2: LB_FWD_CASE(__nv_bfloat16, 2);
+                      case 3: LB_FWD_CASE(__nv_bfloat16, 3); case 4: LB_FWD_CASE(__nv_bfloat16, 4); }
+    } else {
+        switch (fr) { case 1: LB_FWD_CASE(float, 1); case 2: LB_FWD_CASE(float, 2);
+                      case 3: LB_FWD_CASE(float, 3); case 4: LB_FWD_CASE(float, 4); }
+    }
+#undef LB_FWD_CASE
+    return cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Scores of one query against the first n stored updates, for reads whose scores were not cached by the writes
+// (a stack built without queries, or a read issued out of write order): dots[i, t] = q . V[i, t, :].
+// Replaces the score half of the reference's online read kernel (fused_dattn.py:426-433).
+// One warp per (token, source) row; grid-stride.
+// ---------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) scores_kernel(const T *__restrict__ V, const float *__restrict__ q,
+                                                     float *__restrict__ dots, long long n_tok, int d, int n) {
+    using S = Store<T>;
+    constexpr int VEC = S::kVec;
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const long long rows = n_tok * n;
+    for (long long row = warp0; row < rows; row += nwarps) {     // row = i * n_tok + t
+        const T *vp = V + row * d;
+        float acc = 0.f;
+        for (int c = lane * VEC; c < d; c += 32 * VEC) {
+            float v[VEC];
+            S::unpack(ld_global_stream_v4(vp + c), v);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc = fmaf(v[e], __ldg(q + c + e), acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) dots[row] = acc;
+    }
+}
+
+cudaError_t launch_scores(int dtype, const void *V, const float *q, float *dots, long long n_tok, int d, int n,
+                          int sms, cudaStream_t stream) {
+    long long rows = n_tok * n;
+    if (rows == 0) return cudaSuccess;
+    long long blocks = (rows + 7) / 8;
+    int grid = (int)(blocks < (long long)sms * 8 ? blocks : (long long)sms * 8);
+    if (dtype == LB_DTYPE_BF16)
+        scores_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(V), q, dots, n_tok, d, n);
+    else
+        scores_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float *>(V), q, dots, n_tok, d, n);
+    return cudaGetLastError();
+}
+
+}  // namespace lb

@@ -1,0 +1,369 @@
+"""Drop-in replacement of the reference's `fused_dattn` module, backed by the sm_100a CUDA kernels.
+
+Same names, argument meaning and error behaviour as the reference module the models import lazily
+(looped_transformer.py:315-331 and the trainer model's `_fused_dattn()`): `rstd`, `fused_read_supported`,
+`FusedDattnRead`, `DattnStack` (+ `write`, `rstd`, `grads`), `_alias`, `FusedDattnReadStk`.  One read at step s has
+n = s + 1 sources, the raw block updates v_i, and computes
+
+    z_i  = r_i (q . v_i) / sqrt(d)                       r_i the key scale of v_i (an input with its own gradient)
+    p    = softmax_i(z_i + lc_i),  p0 = softmax_i(lc_i)   lc_i = log max(c0_i, 1e-8),  M = sum_i c0_i
+    tc_i = c0_i + M (p_i - p0_i)                          the installed coefficients, returned for the next read
+    out  = base + sum_i (tc_i - cbar_i) v_i               cbar_i the coefficients installed by the previous read
+
+exactly as the reference read (LoopDeltaAttnRes.combine, looped_transformer.py:405-424).  Differences from the
+reference module are confined to private details: the score cache DOTS is laid out [query][update][token], only the
+queries that will read an update are scored at its write, the log-prior and the mass are formed inside the kernels,
+and the backward is one kernel.  There is no CPU or eager fallback: unsupported inputs raise.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, ptr, stream_ptr
+
+__all__ = ["rstd", "fused_read_supported", "FusedDattnRead", "DattnStack", "_alias", "FusedDattnReadStk"]
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"loopback_b200.{what}: tensors must live on a CUDA device (there is no CPU path)")
+
+
+# --------------------------------------------------------------------------------------------------------------
+# the key scale of a free-standing update (list layout)            reference: fused_dattn.py:197-261
+# --------------------------------------------------------------------------------------------------------------
+class _Rstd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, eps: float):
+        xc = x.contiguous()
+        d = xc.shape[-1]
+        n_tok = xc.numel() // d
+        r = torch.empty(xc.shape[:-1] + (1,), device=xc.device, dtype=torch.float32)
+        with torch.cuda.device(xc.device):
+            check(_lib.lib().lb_rstd_fwd(ptr(xc), ptr(r), n_tok, d, float(eps), dtype_code(xc.dtype), stream_ptr()),
+                  "rstd")
+        ctx.save_for_backward(xc, r)
+        return r
+
+    @staticmethod
+    def backward(ctx, gr: torch.Tensor):
+        xc, r = ctx.saved_tensors
+        d = xc.shape[-1]
+        n_tok = xc.numel() // d
+        gx = torch.empty_like(xc)
+        grc = gr.contiguous().float()
+        with torch.cuda.device(xc.device):
+            check(_lib.lib().lb_rstd_bwd(ptr(xc), ptr(r), ptr(grc), ptr(gx), n_tok, d, dtype_code(xc.dtype),
+                                         stream_ptr()), "rstd backward")
+        return gx, None
+
+
+def rstd(delta: torch.Tensor, eps: float) -> torch.Tensor:
+    """The RMSNorm scale of a source, (b, t, 1) fp32, differentiable: the key of the read is delta * rstd."""
+    _require_cuda(delta, "rstd")
+    return _Rstd.apply(delta, float(eps))
+
+
+def fused_read_supported(base, values, rstds, cbar) -> bool:
+    """CUDA, contiguous, same-shape same-dtype bf16/fp32 sources and base; contiguous fp32 (b, t, 1) rstds and a
+    contiguous fp32 (b, t, n) cbar.  Same predicate as the reference (fused_dattn.py:379-395), plus the kernels' own
+    limits (row size a multiple of 16 bytes, at most 128 sources)."""
+    v0 = values[0]
+    if not v0.is_cuda or v0.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    shape = v0.shape
+    if base.dtype != v0.dtype or base.shape != shape:
+        return False
+    for v in values:
+        if v.dtype != v0.dtype or v.shape != shape or not v.is_contiguous():
+            return False
+    rshape = shape[:-1] + (1,)
+    for r in rstds:
+        if r.dtype != torch.float32 or r.shape != rshape or not r.is_contiguous():
+            return False
+    if (shape[-1] * v0.element_size()) % 16 != 0 or shape[-1] * v0.element_size() > 16384:
+        return False
+    if len(values) > _lib.LB_MAX_SOURCES:
+        return False
+    return cbar.dtype == torch.float32 and cbar.shape == shape[:-1] + (len(values),) and cbar.is_contiguous()
+
+
+# --------------------------------------------------------------------------------------------------------------
+# shared launch helpers
+# --------------------------------------------------------------------------------------------------------------
+def _launch_read_fwd(V, R, dots, qi, base, cbar, c0, n_tok, d, N, n, save):
+    dev = V.device
+    out = torch.empty_like(base)
+    tc = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
+    lg = lse = lse0 = None
+    if save:
+        lg = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
+        lse = torch.empty(n_tok, device=dev, dtype=torch.float32)
+        lse0 = torch.empty(n_tok, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev), _timed("read_fwd", n):
+        check(_lib.lib().lb_read_fwd(ptr(V), ptr(R), ptr(dots), int(qi), ptr(base), ptr(cbar), ptr(c0), ptr(out),
+                                     ptr(tc), ptr(lg), ptr(lse), ptr(lse0), n_tok, d, N, n, dtype_code(V.dtype),
+                                     stream_ptr()), "read forward")
+    return out, tc, lg, lse, lse0
+
+
+def _scratch_for(d: int, device) -> torch.Tensor:
+    nbytes = int(_lib.lib().lb_read_bwd_scratch_bytes(int(d)))
+    return torch.empty(nbytes // 4, device=device, dtype=torch.float32)
+
+
+# Optional timing hook: a callable(kind, n, accum) -> context manager wrapped around the big launches; the benchmark
+# installs one that brackets each launch with CUDA events on the launching stream. None = no overhead.
+LAUNCH_TIMER = None
+
+
+class _NoTimer:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def _timed(kind, n, accum=False):
+    return _NoTimer() if LAUNCH_TIMER is None else LAUNCH_TIMER(kind, n, accum)
+
+
+def _launch_read_bwd(V, R, dV, dR, qc, g, gt, cbar, c0, lg, lse, lse0, scratch, n_tok, d, N, n, accum):
+    dev = V.device
+    dcbar = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
+    dq = torch.empty(d, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev), _timed("read_bwd", n, accum):
+        check(_lib.lib().lb_read_bwd(ptr(V), ptr(R), ptr(dV), ptr(dR), ptr(qc), ptr(g), ptr(gt), ptr(cbar), ptr(c0),
+                                     ptr(lg), ptr(lse), ptr(lse0), ptr(dcbar), ptr(dq), ptr(scratch), n_tok, d, N, n,
+                                     int(bool(accum)), dtype_code(V.dtype), stream_ptr()), "read backward")
+    return dq, dcbar
+
+
+# --------------------------------------------------------------------------------------------------------------
+# list layout: one tensor per source                                reference: fused_dattn.py:264-334
+# --------------------------------------------------------------------------------------------------------------
+class FusedDattnRead(torch.autograd.Function):
+    """(out, tc) = FusedDattnRead.apply(q, base, cbar, c0, *values, *rstds).
+
+    The kernels index one stack, so the n sources are gathered into a temporary stack first (one extra copy of the
+    sources per read; the stacked layout below avoids it and is the path the trainer uses)."""
+
+    @staticmethod
+    def forward(ctx, q, base, cbar, c0, *srcs):
+        n = len(srcs) // 2
+        values, rstds = srcs[:n], srcs[n:]
+        cbar_c = cbar.detach().float().contiguous()
+        if not fused_read_supported(base, values, rstds, cbar_c):
+            raise RuntimeError("loopback_b200.FusedDattnRead: unsupported layout (see fused_read_supported)")
+        v0 = values[0]
+        d = v0.shape[-1]
+        n_tok = v0.numel() // d
+        dev = v0.device
+        Vt = torch.stack([v.detach() for v in values])                       # [n, ..., d]
+        Rt = torch.stack([r.detach().reshape(n_tok) for r in rstds])         # [n, n_tok]
+        qc = q.detach().float().contiguous()
+        c0c = c0.detach().float().contiguous()
+        base_c = base.detach().contiguous()
+        dots = torch.empty((n, n_tok), device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev):
+            check(_lib.lib().lb_scores(ptr(Vt), ptr(qc), ptr(dots), n_tok, d, n, n, dtype_code(Vt.dtype),
+                                       stream_ptr()), "scores")
+        save = any(ctx.needs_input_grad)         # no graph (inference): the backward's saves are not written
+        out, tc, lg, lse, lse0 = _launch_read_fwd(Vt, Rt, dots, 0, base_c, cbar_c, c0c, n_tok, d, n, n, save=save)
+        if save:
+            ctx.save_for_backward(qc, cbar_c, c0c, lg, lse, lse0, Vt, Rt)
+        ctx.n, ctx.q_dtype, ctx.base_shape = n, q.dtype, base.shape
+        ctx.rshape = rstds[0].shape
+        return out, tc.view(*base.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, g, gt):
+        qc, cbar_c, c0c, lg, lse, lse0, Vt, Rt = ctx.saved_tensors
+        n = ctx.n
+        d = Vt.shape[-1]
+        n_tok = Vt[0].numel() // d
+        g = g.contiguous()
+        gt_c = None if gt is None else gt.reshape(n_tok, n).float().contiguous()
+        dVt = torch.empty_like(Vt)
+        dRt = torch.empty_like(Rt)
+        scratch = _scratch_for(d, Vt.device)
+        dq, dcbar = _launch_read_bwd(Vt, Rt, dVt, dRt, qc, g, gt_c, cbar_c, c0c, lg, lse, lse0, scratch, n_tok, d, n, n,
+                                     accum=False)
+        return (dq.to(ctx.q_dtype), g, dcbar.view(*ctx.base_shape[:-1], n), None,
+                *dVt.unbind(0), *[dRt[i].view(ctx.rshape) for i in range(n)])
+
+
+# --------------------------------------------------------------------------------------------------------------
+# stacked layout                                                    reference: fused_dattn.py:398-409, :629-793
+# --------------------------------------------------------------------------------------------------------------
+def _alias(stack_tensor: torch.Tensor, s: int) -> torch.Tensor:
+    """Slice s of a stack as a tensor that shares its storage but is not an autograd view of it: later slices are
+    written in place, and autograd forbids a custom Function to return a view whose base is then modified."""
+    sl = stack_tensor[s]
+    out = torch.empty(0, dtype=stack_tensor.dtype, device=stack_tensor.device)
+    out.set_(stack_tensor.untyped_storage(), sl.storage_offset(), sl.shape, sl.stride())
+    return out
+
+
+class DattnStack:
+    """The stacked storage of one forward pass: V[n_steps, b, t, d] (the updates), R[n_steps, b, t, 1] (their key
+    scales) and, from the first backward on, their gradient stacks dV / dR.  Given `query` (the read queries,
+    (n_steps - 1, d); read s uses row s - 1) each write also stores the update's scores against the queries of the
+    reads that will see it, DOTS[query, update, token] fp32, and the reads use those; the queries are taken as they
+    are when the stack is built, i.e. for one forward pass."""
+    __slots__ = ("V", "R", "dV", "dR", "n_steps", "n_tok", "d", "eps", "Q", "QT", "DOTS", "r_done", "_scratch")
+
+    def __init__(self, n_steps: int, shape, dtype, device, query=None, eps: float = 1e-6):
+        b, t, d = shape
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError("loopback_b200.DattnStack: device must be a CUDA device (there is no CPU path)")
+        dtype_code(dtype)
+        if (d * torch.empty(0, dtype=dtype).element_size()) % 16 != 0:
+            raise RuntimeError(f"loopback_b200.DattnStack: row size of d={d} {dtype} is not a multiple of 16 bytes")
+        if n_steps > _lib.LB_MAX_SOURCES:
+            raise RuntimeError(f"loopback_b200.DattnStack: at most {_lib.LB_MAX_SOURCES} steps, got {n_steps}")
+        self.n_steps, self.n_tok, self.d = int(n_steps), b * t, d
+        self.V = torch.empty((n_steps, b, t, d), dtype=dtype, device=device)
+        self.R = torch.empty((n_steps, b, t, 1), dtype=torch.float32, device=device)
+        self.dV = self.dR = None
+        self.eps = float(eps)
+        self.r_done = [False] * self.n_steps      # R[s] (and the scores of update s) written by the write of s
+        self.Q = self.QT = self.DOTS = None
+        self._scratch = None
+        if query is not None:
+            self.Q = query.detach().float().contiguous()
+            self.DOTS = torch.empty((max(1, self.Q.shape[0]), self.n_steps, b * t), dtype=torch.float32, device=device)
+
+    def write(self, s: int, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """V[s] = h - x, returned as the update tensor (sharing the stack's storage, with the autograd edge to h
+        and x)."""
+        return _WriteDelta.apply(self, s, h, x)
+
+    def rstd(self, s: int, delta: torch.Tensor, eps: float) -> torch.Tensor:
+        """R[s] = the key scale of V[s], returned sharing the stack's storage (differentiable through `delta`)."""
+        return _RstdStk.apply(self, s, delta, float(eps))
+
+    def grads(self):
+        if self.dV is None:
+            self.dV = torch.empty_like(self.V)
+            self.dR = torch.empty_like(self.R)
+            return False
+        return True
+
+    def scratch(self) -> torch.Tensor:
+        if self._scratch is None:
+            self._scratch = _scratch_for(self.d, self.V.device)
+        return self._scratch
+
+
+class _WriteDelta(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, stack: DattnStack, s: int, h: torch.Tensor, x: torch.Tensor):
+        if not 0 <= s < stack.n_steps:
+            raise RuntimeError(f"delta_attnres stacked write: step {s} outside [0, {stack.n_steps})")
+        if h.dtype != stack.V.dtype or x.dtype != stack.V.dtype:
+            raise RuntimeError("delta_attnres stacked write: h and x must have the stack's dtype")
+        if h.numel() != stack.n_tok * stack.d or x.numel() != stack.n_tok * stack.d:
+            raise RuntimeError("delta_attnres stacked write: h and x must have the stack's shape")
+        out = _alias(stack.V, s)
+        hc, xc = h.detach().contiguous(), x.detach().contiguous()
+        nq = 0 if stack.Q is None else stack.Q.shape[0]
+        with torch.cuda.device(stack.V.device), _timed("write", s):
+            check(_lib.lib().lb_write(ptr(hc), ptr(xc), ptr(stack.V), ptr(stack.R), ptr(stack.Q), ptr(stack.DOTS),
+                                      stack.n_tok, stack.d, stack.n_steps, nq, int(s), stack.eps,
+                                      dtype_code(stack.V.dtype), stream_ptr()), "write")
+        stack.r_done[s] = True
+        return out
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        gc = g.contiguous()
+        dx = torch.empty_like(gc)
+        with torch.cuda.device(gc.device):
+            check(_lib.lib().lb_write_bwd_dx(ptr(gc), ptr(dx), gc.numel(), dtype_code(gc.dtype), stream_ptr()),
+                  "write backward")
+        return None, None, g, dx
+
+
+class _RstdStk(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, stack: DattnStack, s: int, x: torch.Tensor, eps: float):
+        r = _alias(stack.R, s)
+        if not (stack.r_done[s] and eps == stack.eps):      # else the write already stored R[s]
+            xc = x.detach().contiguous()
+            with torch.cuda.device(xc.device):
+                check(_lib.lib().lb_rstd_fwd(ptr(xc), ptr(r), stack.n_tok, stack.d, float(eps), dtype_code(xc.dtype),
+                                             stream_ptr()), "stacked rstd")
+        ctx.stack, ctx.s, ctx.x = stack, s, x
+        return r
+
+    @staticmethod
+    def backward(ctx, gr: torch.Tensor):
+        stack, s, x = ctx.stack, ctx.s, ctx.x
+        if stack.dV is None:
+            raise RuntimeError("delta_attnres stacked read: the scale's backward ran before any read's backward")
+        grc = gr.contiguous().float()
+        xc = x.detach().contiguous()
+        dv_s = stack.dV[s]
+        with torch.cuda.device(xc.device):
+            check(_lib.lib().lb_rstd_bwd_acc(ptr(xc), ptr(stack.R[s]), ptr(grc), ptr(dv_s), stack.n_tok, stack.d,
+                                             dtype_code(xc.dtype), stream_ptr()), "stacked rstd backward")
+        out = _alias(stack.dV, s)
+        ctx.stack = ctx.x = None          # release the stack from this node
+        return None, None, out, None
+
+
+class FusedDattnReadStk(torch.autograd.Function):
+    """(out, tc) = apply(stack, step, q, base, cbar, c0, *updates, *scales): the updates and scales are the stack's
+    slices 0..step (inputs only for autograd's bookkeeping; the kernels read the stack)."""
+
+    @staticmethod
+    def forward(ctx, stack: DattnStack, step: int, q, base, cbar, c0, *srcs):
+        n = len(srcs) // 2
+        d, n_tok, dev = stack.d, stack.n_tok, stack.V.device
+        if base.dtype != stack.V.dtype or not base.is_contiguous() or base.shape[:-1] != stack.V.shape[1:3]:
+            raise RuntimeError("delta_attnres stacked read: base must be contiguous, the stack's dtype and shape")
+        qc = q.detach().float().contiguous()
+        c0c = c0.detach().float().contiguous()
+        cbar_c = cbar.detach().float().contiguous()
+        if stack.DOTS is not None and step >= 1 and all(stack.r_done[:n]):
+            dots, qi = stack.DOTS, step - 1           # the stored scores of query step - 1 (q is that query)
+        else:
+            dots, qi = torch.empty((stack.n_steps, n_tok), device=dev, dtype=torch.float32), 0
+            with torch.cuda.device(dev):
+                check(_lib.lib().lb_scores(ptr(stack.V), ptr(qc), ptr(dots), n_tok, d, stack.n_steps, n,
+                                           dtype_code(stack.V.dtype), stream_ptr()), "scores")
+        save = any(ctx.needs_input_grad)         # no graph (inference): the backward's saves are not written
+        out, tc, lg, lse, lse0 = _launch_read_fwd(stack.V, stack.R, dots, qi, base.detach(), cbar_c, c0c, n_tok, d,
+                                                  stack.n_steps, n, save=save)
+        if save:
+            ctx.save_for_backward(qc, cbar_c, c0c, lg, lse, lse0)
+        ctx.stack, ctx.step, ctx.n, ctx.q_dtype, ctx.base_shape = stack, int(step), n, q.dtype, base.shape
+        return out, tc.view(*base.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor, gt):
+        qc, cbar_c, c0c, lg, lse, lse0 = ctx.saved_tensors
+        stack, step, n = ctx.stack, ctx.step, ctx.n
+        d, n_tok = stack.d, stack.n_tok
+        accum = stack.grads()
+        g = g.contiguous()
+        gt_c = None if gt is None else gt.reshape(n_tok, n).float().contiguous()
+        dq, dcbar = _launch_read_bwd(stack.V, stack.R, stack.dV, stack.dR, qc, g, gt_c, cbar_c, c0c, lg, lse, lse0,
+                                     stack.scratch(), n_tok, d, stack.n_steps, n, accum)
+        final = [i == step or (step == 1 and i == 0) for i in range(n)]   # the last read of scale i, in backward order
+        grads = (None, None, dq.to(ctx.q_dtype), g, dcbar.view(*ctx.base_shape[:-1], n), None,
+                 *[None] * n, *[_alias(stack.dR, i) if final[i] else None for i in range(n)])
+        # Release the stack from this node: ctx attributes live as long as the graph node, and a training loop that
+        # keeps each micro-batch's loss until the optimizer step would otherwise keep every micro-batch's stack.
+        ctx.stack = None
+        return grads
+
+
+def device_error(clear: bool = True) -> int:
+    """Synchronise and return the kernels' error word (0 = no bounded wait ran out); see lb_device_error."""
+    return _lib.device_error(clear)
+
