@@ -72,11 +72,11 @@ def test_write_matches_oracle(L, dtype, n_tok, d):
     for s in range(N):
         v_ref, r_ref = CO.write(hs[s].float().numpy(), x.float().numpy(), 1e-6, dtype == torch.bfloat16)
         assert torch.equal(V[s].float().cpu(), torch.from_numpy(v_ref)), "the stored update must be bit-exact"
-        assert rel(R[s], r_ref) < 2e-6
+        assert rel(R[s], r_ref) < TOL32
         j0 = max(s - 1, 0)
         want = torch.from_numpy(v_ref).double() @ Q.double().t()          # [n_tok, NQ]
         got = DOTS[:, s, :].t().cpu()
-        assert rel(got[:, j0:], want[:, j0:]) < 2e-6
+        assert rel(got[:, j0:], want[:, j0:]) < TOL32
         assert torch.isnan(got[:, :j0]).all(), "queries that never read update s must not be scored"
 
 
@@ -130,6 +130,17 @@ def run_read_oracle(deltas, proposal, h0, q, prior, coeffs, up, up2, boundary, h
                 dh0=hh.grad if hh.grad is not None else zero, dcoef=cf.grad)
 
 
+def teacher_forced_out(ins, boundary, beta=0.75):
+    """The read evaluated in fp64 on exactly what the kernel is given: the storage-dtype sources and the base as its
+    caller forms it (the boundary blend is the caller's torch arithmetic in the storage dtype, looped_transformer.py:381)."""
+    deltas, proposal, h0, q, prior, coeffs, up, up2 = ins
+    base_st = proposal + beta * (h0 - proposal) if boundary else proposal
+    _, cbar, c0 = TO.prologue(proposal.double(), h0.double(), coeffs.double(), prior.double(), beta, boundary)
+    with torch.no_grad():
+        out, tc = TO.read(base_st.double(), [x.double() for x in deltas], q.double(), cbar, c0, 1e-6, accumulate="exact")
+    return out, tc
+
+
 SHAPES32 = [(2, 64, 768), (2, 37, 1024), (1, 50, 1536), (1, 9, 3072), (1, 5, 64), (3, 7, 2048)]
 
 
@@ -156,8 +167,9 @@ def test_read_bf16_against_fp64(FD, b, t, d, n):
     got = run_read_gpu(FD, *ins, True)
     ref_bf16 = run_read_oracle(*ins, True, torch.bfloat16, "storage")      # the reference's own arithmetic
     want = run_read_oracle(*ins, True, torch.float64, "exact")
-    rms = float(want["out"].pow(2).mean().sqrt())
-    err_out = float((got["out"].double().cpu() - want["out"]).abs().max())
+    out_tf, _ = teacher_forced_out(ins, True)
+    rms = float(out_tf.pow(2).mean().sqrt())
+    err_out = float((got["out"].double().cpu() - out_tf).abs().max())
     assert err_out <= 2e-2 * rms, (err_out, rms)
     assert rel(got["tc"], want["tc"]) < 1e-4
     for k in want:
@@ -207,7 +219,11 @@ def test_golden_single_reads(FD, case):
                 continue
             assert rel(got[k], want) < TOL32, (k, rel(got[k], want))
     else:
-        want32 = READS[f"{name}/ref32/out"]
+        # the reference's fp32 evaluation, moved onto the bf16 base the kernel is actually given (out = base + sum)
+        proposal, h0 = ins[1], ins[2]
+        base_bf16 = proposal + 0.75 * (h0 - proposal) if boundary else proposal
+        base_f32 = proposal.float() + 0.75 * (h0.float() - proposal.float()) if boundary else proposal.float()
+        want32 = READS[f"{name}/ref32/out"] + (base_bf16.float() - base_f32).numpy()
         rms = float(np.sqrt((want32.astype(np.float64) ** 2).mean()))
         assert float(np.abs(got["out"].float().cpu().numpy() - want32).max()) <= 2e-2 * rms
         assert rel(got["tc"], READS[f"{name}/ref32/tc"]) < 1e-4
