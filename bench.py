@@ -190,6 +190,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on small cases)")
+    ap.add_argument("--opt", action="append", default=[], help="library tuning knob name=value (lb_set_option)")
+    ap.add_argument("--detail", default="", help="write per-launch timings (kind, n, GB/s) to this file")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.tokens:
@@ -215,6 +217,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     L.lib()
+    for kv in args.opt:
+        name, val = kv.split("=")
+        L.set_option(name, int(val))
 
     N, d = w["K"] * w["R"], w["d"]
     n_tok = w["b"] * w["t"]
@@ -287,6 +292,18 @@ def main():
         acc[0] += units * n_tok * d * elem
         acc[1] += ms * 1e-3
         acc[2] += 1
+    if args.detail and rank == 0:
+        rows = {}
+        for kind, n, accum, a, b_ in launches:
+            units = (n + (2 * n if accum else n) + 1) if kind == "read_bwd" else ((n + 2) if kind == "read_fwd" else 3)
+            r = rows.setdefault((kind, n, bool(accum)), [0.0, 0, units])
+            r[0] += a.elapsed_time(b_)
+            r[1] += 1
+        with open(args.detail, "w") as f:
+            f.write("kind n accum launches ms_avg algorithmic_GBs frac_of_peak\n")
+            for (kind, n, accum), (ms, cnt, units) in sorted(rows.items()):
+                gbs = units * n_tok * d * elem / (ms / cnt * 1e-3) / 1e9
+                f.write(f"{kind} {n} {int(accum)} {cnt} {ms / cnt:.4f} {gbs:.1f} {gbs / peak:.3f}\n")
     dominant = max(per_kind, key=lambda k: per_kind[k][1]) if per_kind else None
     roofline = None
     kernels = {}

@@ -36,7 +36,8 @@ int cuda_fail(cudaError_t e, const char *what) {
 }
 
 struct Options {
-    int fwd_stages = 0, bwd_stages = 0, fwd_fr = 0, grid_cap = 0;
+    int fwd_stages = 0, bwd_stages = 0, fwd_fr = 0, grid_cap = 0, fwd_warps = 0, bwd_warps = 0, bwd_wpt = 0,
+        tma_per_chunk = 0;
 } g_opt;
 
 struct DeviceInfo {
@@ -85,16 +86,39 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     return fn;
 }
 
-// A tiled descriptor over [outer][n_tok][d] (outer == 0: rank 2), box = 512 bytes x box_tok tokens.
-int make_map(CUtensorMap *m, const void *base, int dtype, long long n_tok, int d, int outer, int box_tok) {
+// A tiled descriptor over [outer][n_tok][d] (outer == 0: no outer dimension).
+//   box_chunks == 0: dimensions (d, n_tok[, outer]), box = 512 bytes x box_tok tokens: one chunk of every token;
+//   box_chunks  > 0: the row is split into whole 512-byte chunks, dimensions (chunk width, chunks, n_tok[, outer]),
+//                    box = 512 bytes x box_chunks chunks x box_tok tokens: a whole tile in one copy, token-major.
+//                    Needs d to be a multiple of the chunk width.
+int make_map(CUtensorMap *m, const void *base, int dtype, long long n_tok, int d, int outer, int box_tok,
+             int box_chunks) {
     auto fn = encode_fn();
     if (!fn) return fail(LB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
-    const cuuint32_t rank = outer > 0 ? 3 : 2;
-    cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)n_tok, (cuuint64_t)(outer > 0 ? outer : 1)};
-    cuuint64_t strides[2] = {(cuuint64_t)d * elem, (cuuint64_t)d * elem * (cuuint64_t)n_tok};
-    cuuint32_t box[3] = {(cuuint32_t)(lb::kChunkBytes / elem), (cuuint32_t)box_tok, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
+    const cuuint64_t bw = lb::kChunkBytes / elem;
+    cuuint64_t dims[4];
+    cuuint64_t strides[3];
+    cuuint32_t box[4];
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    cuuint32_t rank = 0;
+    if (box_chunks > 0) {
+        dims[0] = bw; dims[1] = (cuuint64_t)d / bw; dims[2] = (cuuint64_t)n_tok;
+        strides[0] = lb::kChunkBytes; strides[1] = (cuuint64_t)d * elem;
+        box[0] = (cuuint32_t)bw; box[1] = (cuuint32_t)box_chunks; box[2] = (cuuint32_t)box_tok;
+        rank = 3;
+    } else {
+        dims[0] = (cuuint64_t)d; dims[1] = (cuuint64_t)n_tok;
+        strides[0] = (cuuint64_t)d * elem;
+        box[0] = (cuuint32_t)bw; box[1] = (cuuint32_t)box_tok;
+        rank = 2;
+    }
+    if (outer > 0) {
+        dims[rank] = (cuuint64_t)outer;
+        strides[rank - 1] = (cuuint64_t)d * elem * (cuuint64_t)n_tok;
+        box[rank] = 1;
+        ++rank;
+    }
     CUresult r = fn(m, dtype == LB_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                     rank, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -149,6 +173,10 @@ int lb_set_option(const char *name, int value) {
     else if (!strcmp(name, "bwd_stages")) g_opt.bwd_stages = value;
     else if (!strcmp(name, "fwd_fr")) g_opt.fwd_fr = value;
     else if (!strcmp(name, "grid_cap")) g_opt.grid_cap = value;
+    else if (!strcmp(name, "fwd_warps")) g_opt.fwd_warps = value;
+    else if (!strcmp(name, "bwd_warps")) g_opt.bwd_warps = value;
+    else if (!strcmp(name, "bwd_wpt")) g_opt.bwd_wpt = value;
+    else if (!strcmp(name, "tma_per_chunk")) g_opt.tma_per_chunk = value;
     else return fail(LB_ERR_ARG, "unknown option '%s'", name);
     return LB_OK;
 }
@@ -254,14 +282,19 @@ int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const 
     if ((rc = device_info(&di))) return rc;
 
     const int nch = chunks_of(d, dtype);
-    const long long tok_tiles = (n_tok + 7) / 8;
+    const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
+    const bool rank4 = !g_opt.tma_per_chunk && (d * elem) % lb::kChunkBytes == 0;
+    int ncw = g_opt.fwd_warps == 8 || g_opt.fwd_warps == 16 ? g_opt.fwd_warps : 16;
+    if (n_tok <= 8 * (long long)di.sms && g_opt.fwd_warps == 0) ncw = 8;      // few tokens: smaller tiles, more CTAs
+    const long long tok_tiles = (n_tok + ncw - 1) / ncw;
     // fragments per warp: the widest tile that wastes no shared memory, narrowed until the grid fills the GPU
     int fr = g_opt.fwd_fr;
     if (fr < 1 || fr > 4) {
         int best = 1, best_waste = 1 << 30;
-        for (int f = 4; f >= 1; --f) {
-            const int cg = (nch + f - 1) / f;
-            const int waste = cg * f - nch;
+        const int fmax = ncw == 16 ? 2 : 4;
+        for (int f = fmax; f >= 1; --f) {
+            const int cgs = (nch + f - 1) / f;
+            const int waste = cgs * f - nch;
             if (waste < best_waste) { best_waste = waste; best = f; }
         }
         fr = best;
@@ -270,11 +303,11 @@ int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const 
     const int cg = (nch + fr - 1) / fr;
     int stages = g_opt.fwd_stages > 0 ? g_opt.fwd_stages : 8;
     if (stages > 12) stages = 12;
-    while (stages > 2 && lb::read_fwd_smem_bytes(fr, stages) > kMaxSmem) --stages;
+    while (stages > 2 && lb::read_fwd_smem_bytes(fr, ncw, stages) > kMaxSmem) --stages;
 
     CUtensorMap tmV, tmB;
-    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, 8))) return rc;
-    if ((rc = make_map(&tmB, base, dtype, n_tok, d, 0, 8))) return rc;
+    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, ncw, rank4 ? fr : 0))) return rc;
+    if ((rc = make_map(&tmB, base, dtype, n_tok, d, 0, ncw, rank4 ? fr : 0))) return rc;
 
     lb::ReadFwdParams p;
     p.R = R;
@@ -282,13 +315,14 @@ int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const 
     p.cbar = cbar; p.c0 = c0; p.out = out; p.TC = TC; p.LG = LG; p.LSE = LSE; p.LSE0 = LSE0;
     p.n_tok = n_tok; p.d = d; p.n = n; p.chunks = nch; p.col_groups = cg; p.tok_tiles = tok_tiles;
     p.stages = stages;
+    p.rank4 = rank4 ? 1 : 0;
     p.inv_sqrt_d = 1.0f / sqrtf((float)d);
     p.err_word = di.err_word;
     const long long tiles = tok_tiles * cg;
     int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
     if (cap > kMaxGrid) cap = kMaxGrid;
     const int grid = (int)(tiles < cap ? tiles : cap);
-    cudaError_t e = lb::launch_read_fwd(dtype, fr, tmV, tmB, p, grid, static_cast<cudaStream_t>(stream));
+    cudaError_t e = lb::launch_read_fwd(dtype, fr, ncw, tmV, tmB, p, grid, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_read_fwd launch");
 }
 
@@ -314,33 +348,43 @@ int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float 
     }
 
     const int nch = chunks_of(d, dtype);
-    int wpt = 1;
-    while (wpt < 8 && (nch + wpt - 1) / wpt > 4) wpt <<= 1;
-    const int fr = (nch + wpt - 1) / wpt;
-    if (fr > 4) return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: d=%d needs more than 32 chunks per row", d);
-    const int bt = 8 / wpt;
+    const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
+    const bool rank4 = !g_opt.tma_per_chunk && (d * elem) % lb::kChunkBytes == 0;
+    const int ncw = g_opt.bwd_warps == 8 ? 8 : 16;
+    // warps per token / fragments per warp: no wasted fragments first, then 2 fragments per warp, then 3, then 1
+    const int fr_max = ncw == 16 ? 3 : 4;
+    int wpt = 0, fr = 0, best_cost = 1 << 30;
+    for (int w = 1; w <= ncw; w <<= 1) {
+        const int f = (nch + w - 1) / w;
+        if (f > fr_max) continue;
+        const int cost = (f * w - nch) * 8 + (f == 2 ? 0 : (f == 3 ? 1 : (f == 1 ? 2 : 3)));
+        if (g_opt.bwd_wpt == w) { wpt = w; fr = f; break; }
+        if (cost < best_cost) { best_cost = cost; wpt = w; fr = f; }
+    }
+    if (wpt == 0) return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: d=%d needs more than %d chunks per row", d, fr_max * ncw);
+    const int bt = ncw / wpt;
     const int vec = dtype == LB_DTYPE_BF16 ? 8 : 4;
     int stages = g_opt.bwd_stages > 0 ? g_opt.bwd_stages : 8;
     if (stages > 12) stages = 12;
-    while (stages > 2 && lb::read_bwd_smem_bytes(fr, wpt, stages, n, vec) > kMaxSmem) --stages;
-    if (lb::read_bwd_smem_bytes(fr, wpt, stages, n, vec) > kMaxSmem)
+    while (stages > 2 && lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec) > kMaxSmem) --stages;
+    if (lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec) > kMaxSmem)
         return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: shared memory does not fit for d=%d, n=%d", d, n);
 
     CUtensorMap tmV, tmG, tmDV;
-    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, bt))) return rc;
-    if ((rc = make_map(&tmG, g, dtype, n_tok, d, 0, bt))) return rc;
-    if ((rc = make_map(&tmDV, dV, dtype, n_tok, d, N, bt))) return rc;
+    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, bt, rank4 ? nch : 0))) return rc;
+    if ((rc = make_map(&tmG, g, dtype, n_tok, d, 0, bt, rank4 ? nch : 0))) return rc;
+    if ((rc = make_map(&tmDV, dV, dtype, n_tok, d, N, bt, rank4 ? nch : 0))) return rc;
 
     lb::ReadBwdParams p;
     p.R = R; p.dR = dR; p.dV = dV; p.q = q; p.gt = gt; p.cbar = cbar; p.c0 = c0; p.LSE = LSE; p.LSE0 = LSE0; p.LG = LG;
     p.dcbar = dcbar; p.dq_part = static_cast<float *>(scratch);
     p.n_tok = n_tok; p.tok_tiles = (n_tok + bt - 1) / bt; p.d = d; p.n = n; p.chunks = nch; p.wpt = wpt;
-    p.stages = stages; p.accum = accum ? 1 : 0; p.inv_sqrt_d = 1.0f / sqrtf((float)d);
+    p.stages = stages; p.rank4 = rank4 ? 1 : 0; p.accum = accum ? 1 : 0; p.inv_sqrt_d = 1.0f / sqrtf((float)d);
     p.err_word = di.err_word;
     int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
     if (cap > kMaxGrid) cap = kMaxGrid;
     const int grid = (int)(p.tok_tiles < cap ? p.tok_tiles : cap);
-    cudaError_t e = lb::launch_read_bwd(dtype, fr, tmV, tmG, tmDV, p, grid, st);
+    cudaError_t e = lb::launch_read_bwd(dtype, fr, ncw, tmV, tmG, tmDV, p, grid, st);
     if (e != cudaSuccess) return cuda_fail(e, "lb_read_bwd launch");
     e = lb::launch_dq_reduce(p.dq_part, grid, dq, d, p.inv_sqrt_d, st);
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_read_bwd dq reduction launch");

@@ -17,7 +17,6 @@ namespace lb {
 
 constexpr int kChunkBytes = 512;          // one TMA box row
 constexpr int kMaxSources = 128;          // n (= sources of a read) the shared-memory scalar tables are sized for
-constexpr int kConsumerWarps = 8;
 
 // ---------------------------------------------------------------------------------------------------------
 // device-side error word: kernels never trap or spin forever; a wait that runs out records where and returns.
@@ -111,6 +110,15 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, u
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3)
+        : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -144,6 +152,27 @@ template <> struct Store<__nv_bfloat16> {
     }
     // the value a store of `x` would hold, back in fp32
     __device__ __forceinline__ static float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+    // the same fragment as element PAIRS, the operand shape of the packed fp32 instructions (fma.rn.f32x2)
+    static constexpr int kPairs = 4;
+    __device__ __forceinline__ static float2 unpack1(uint32_t u) {
+        return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+    }
+    __device__ __forceinline__ static void unpack2(const uint4 &u, float2 (&f)[4]) {
+        f[0] = unpack1(u.x); f[1] = unpack1(u.y); f[2] = unpack1(u.z); f[3] = unpack1(u.w);
+    }
+    __device__ __forceinline__ static uint4 pack2v(const float2 (&f)[4]) {
+        return make_uint4(pack2(f[0].x, f[0].y), pack2(f[1].x, f[1].y), pack2(f[2].x, f[2].y), pack2(f[3].x, f[3].y));
+    }
+    // round(prev + round(o)) per element: o is rounded to bf16, then one native bf16 add (exact sum, one rounding)
+    __device__ __forceinline__ static uint32_t hadd(uint32_t a, uint32_t b) {
+        __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
+    __device__ __forceinline__ static uint4 accum(const uint4 &prev, const float2 (&o)[4]) {
+        const uint4 r = pack2v(o);
+        return make_uint4(hadd(prev.x, r.x), hadd(prev.y, r.y), hadd(prev.z, r.z), hadd(prev.w, r.w));
+    }
 };
 
 template <> struct Store<float> {
@@ -159,6 +188,23 @@ template <> struct Store<float> {
                           __float_as_uint(f[3]));
     }
     __device__ __forceinline__ static float round(float x) { return x; }
+
+    static constexpr int kPairs = 2;
+    __device__ __forceinline__ static void unpack2(const uint4 &u, float2 (&f)[2]) {
+        f[0] = make_float2(__uint_as_float(u.x), __uint_as_float(u.y));
+        f[1] = make_float2(__uint_as_float(u.z), __uint_as_float(u.w));
+    }
+    __device__ __forceinline__ static uint4 pack2v(const float2 (&f)[2]) {
+        return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x),
+                          __float_as_uint(f[1].y));
+    }
+    __device__ __forceinline__ static uint4 accum(const uint4 &prev, const float2 (&o)[2]) {
+        float2 pf[2];
+        unpack2(prev, pf);
+        pf[0] = __fadd2_rn(pf[0], o[0]);
+        pf[1] = __fadd2_rn(pf[1], o[1]);
+        return pack2v(pf);
+    }
 };
 
 __device__ __forceinline__ uint4 ld_shared_v4(const void *p) {
@@ -195,59 +241,6 @@ __device__ __forceinline__ float group_sum(float v, int width) {
 __device__ __forceinline__ float group_max(float v, int width) {
     for (int o = width >> 1; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// the per-read prior tables every kernel derives from c0 (n floats in device memory):
-//   lc_i = log(max(c0_i, 1e-8)), mass = sum_i c0_i, lse0 = logsumexp(lc), p0_i = exp(lc_i - lse0)
-// computed by one warp with the SAME instruction sequence that the scored softmax uses, so that a zero query
-// gives p == p0 bit for bit.
-// ---------------------------------------------------------------------------------------------------------
-struct PriorTables {
-    float c0[kMaxSources];
-    float lc[kMaxSources];
-    float p0[kMaxSources];
-    float mass;
-    float lse0;
-};
-
-// log-sum-exp over the n values held as x[k] for source i = lane + 32 k; every lane returns the result
-__device__ __forceinline__ float warp_lse(const float (&x)[kMaxSources / 32], int n, int lane) {
-    float mx = -INFINITY;
-#pragma unroll
-    for (int k = 0; k < kMaxSources / 32; ++k)
-        if (lane + 32 * k < n) mx = fmaxf(mx, x[k]);
-    mx = group_max(mx, 32);
-    float s = 0.f;
-#pragma unroll
-    for (int k = 0; k < kMaxSources / 32; ++k)
-        if (lane + 32 * k < n) s += expf(x[k] - mx);
-    s = group_sum(s, 32);
-    return mx + logf(s);
-}
-
-__device__ __forceinline__ void build_prior_tables(PriorTables *pt, const float *__restrict__ c0, int n, int lane) {
-    float lc[kMaxSources / 32], c[kMaxSources / 32];
-    float m = 0.f;
-#pragma unroll
-    for (int k = 0; k < kMaxSources / 32; ++k) {
-        int i = lane + 32 * k;
-        c[k] = i < n ? c0[i] : 0.f;
-        lc[k] = logf(fmaxf(c[k], 1e-8f));
-        m += c[k];
-    }
-    m = group_sum(m, 32);
-    float lse0 = warp_lse(lc, n, lane);
-#pragma unroll
-    for (int k = 0; k < kMaxSources / 32; ++k) {
-        int i = lane + 32 * k;
-        if (i < n) {
-            pt->c0[i] = c[k];
-            pt->lc[i] = lc[k];
-            pt->p0[i] = expf(lc[k] - lse0);
-        }
-    }
-    if (lane == 0) { pt->mass = m; pt->lse0 = lse0; }
 }
 
 }  // namespace lb

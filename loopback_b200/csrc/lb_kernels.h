@@ -26,14 +26,15 @@ struct ReadFwdParams {
     int n;
     int chunks;            // ceil(d * elem / 512)
     int col_groups;        // ceil(chunks / FR)
-    long long tok_tiles;   // ceil(n_tok / 8)
+    long long tok_tiles;   // ceil(n_tok / tokens per tile)
+    int rank4;             // 1: one 4-D TMA box per stage (d a multiple of the chunk width), 0: one box per chunk
     int stages;
     float inv_sqrt_d;
     int *err_word;         // device error word (see lb_device_error)
 };
 
-size_t read_fwd_smem_bytes(int fr, int stages);
-cudaError_t launch_read_fwd(int dtype, int fr, const CUtensorMap &tmV, const CUtensorMap &tmBase,
+size_t read_fwd_smem_bytes(int fr, int ncw, int stages);
+cudaError_t launch_read_fwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmBase,
                             const ReadFwdParams &p, int grid, cudaStream_t stream);
 cudaError_t launch_scores(int dtype, const void *V, const float *q, float *dots, long long n_tok, int d, int n,
                           int sms, cudaStream_t stream);
@@ -79,15 +80,16 @@ struct ReadBwdParams {
     int d;
     int n;
     int chunks;
-    int wpt;               // warps per token (1, 2, 4 or 8); tokens per tile = 8 / wpt
+    int wpt;               // warps per token (a power of two); tokens per tile = consumer warps / wpt
+    int rank4;             // as in ReadFwdParams
     int stages;
     int accum;             // 0: dV / dR are written; 1: added into
     float inv_sqrt_d;
     int *err_word;
 };
 
-size_t read_bwd_smem_bytes(int fr, int wpt, int stages, int n, int vec);
-cudaError_t launch_read_bwd(int dtype, int fr, const CUtensorMap &tmV, const CUtensorMap &tmG,
+size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec);
+cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmG,
                             const CUtensorMap &tmDV, const ReadBwdParams &p, int grid, cudaStream_t stream);
 cudaError_t launch_dq_reduce(const float *dq_part, int rows, float *dq, int d, float scale, cudaStream_t stream);
 

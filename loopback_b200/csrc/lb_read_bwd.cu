@@ -13,25 +13,25 @@
 // :761-793): no GD / SACC round trip through HBM, g is read once, and the query gradient leaves the kernel as one
 // partial row per CTA.
 //
-// Tiles are (8 / WPT) tokens x the full row; a token's row is split over WPT consumer warps (FR chunks of 512 B
-// each). Warp roles as in the forward read: 8 consumer warps, 1 TMA producer lane, 2 scalar warps that prepare the
-// per-(token, source) tables of the next tile. All waits are bounded.
+// Tiles are BT = NCW / WPT tokens x the full row; a token's row is split over WPT consumer warps (FR chunks of
+// 512 B each). Warp roles: NCW consumer warps, 1 TMA producer lane, 2 scalar warps that prepare the
+// per-(token, source) tables of the next tile. The element math runs on pairs (fma.rn.f32x2). All waits are bounded.
 #include "lb_common.cuh"
 #include "lb_kernels.h"
 
 namespace lb {
 
 constexpr int kBwdScalarWarps = 2;
-constexpr int kBwdThreads = (kConsumerWarps + 1 + kBwdScalarWarps) * 32;
 constexpr int kBwdMaxStages = 12;
 constexpr int kBwdTables = 6;     // P, R, GT, W, ZL, DRP
+constexpr int kBwdMaxNcw = 16;
 
 struct BwdSmemTail {
     float c0[kMaxSources];
     float lc[kMaxSources];
     float mass;
     int abort_flag;
-    float xch[2][kConsumerWarps];               // partial g.v of the token's warps, double buffered by source
+    float xch[2][kBwdMaxNcw];                   // partial g.v of the token's warps, double buffered by source
     uint64_t full[kBwdMaxStages];
     uint64_t empty[kBwdMaxStages];
     uint64_t sfull[2];
@@ -40,45 +40,46 @@ struct BwdSmemTail {
 
 // dynamic shared memory: [stages][tables 2 x 6 x n_pad*BT][gdkq n_pad*BT][dq slots][tail]
 __host__ __device__ inline int bwd_npad(int n) { return (n + 3) & ~3; }
-__host__ __device__ inline size_t bwd_table_floats(int n, int wpt) { return (size_t)bwd_npad(n) * (kConsumerWarps / wpt); }
+__host__ __device__ inline size_t bwd_table_floats(int n, int bt) { return (size_t)bwd_npad(n) * bt; }
 
-size_t read_bwd_smem_bytes(int fr, int wpt, int stages, int n, int vec) {
-    size_t stage = (size_t)fr * kConsumerWarps * kChunkBytes;
-    size_t tables = (2 * kBwdTables + 1) * bwd_table_floats(n, wpt) * sizeof(float);
-    size_t slots = (size_t)fr * vec * sizeof(float) * kConsumerWarps * 32;
+size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec) {
+    size_t stage = (size_t)fr * ncw * kChunkBytes;
+    size_t tables = (2 * kBwdTables + 1) * bwd_table_floats(n, ncw / wpt) * sizeof(float);
+    size_t slots = (size_t)fr * vec * sizeof(float) * ncw * 32;
     return 1024 + stages * stage + ((tables + 15) & ~size_t(15)) + slots + sizeof(BwdSmemTail) + 64;
 }
 
-template <typename T, int FR>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <typename T, int FR, int NCW>
+__global__ void __launch_bounds__((NCW + 1 + kBwdScalarWarps) * 32, 1)
 read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
                 const __grid_constant__ CUtensorMap tmDV, ReadBwdParams p) {
     using S = Store<T>;
     constexpr int VEC = S::kVec;
+    constexpr int P = S::kPairs;
     constexpr int V4 = VEC / 4;
     constexpr int BW = kChunkBytes / S::kBytes;
-    constexpr int kStageBytes = FR * kConsumerWarps * kChunkBytes;
+    constexpr int kStageBytes = FR * NCW * kChunkBytes;
+    constexpr int kConsumerThreads = NCW * 32;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int NS = p.stages, n = p.n, WPT = p.wpt, BT = kConsumerWarps / WPT;
-    const size_t tfl = bwd_table_floats(n, WPT);
+    const int NS = p.stages, n = p.n, WPT = p.wpt, BT = NCW / WPT;
+    const size_t tfl = bwd_table_floats(n, BT);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float *tables = reinterpret_cast<float *>(stages + (size_t)NS * kStageBytes);
     float *gdkq = tables + 2 * kBwdTables * tfl;
-    float4 *slots = reinterpret_cast<float4 *>(
-        (reinterpret_cast<uintptr_t>(gdkq + tfl) + 15) & ~uintptr_t(15));
+    float4 *slots = reinterpret_cast<float4 *>((reinterpret_cast<uintptr_t>(gdkq + tfl) + 15) & ~uintptr_t(15));
     BwdSmemTail *sm = reinterpret_cast<BwdSmemTail *>(
-        (reinterpret_cast<uintptr_t>(slots + (size_t)FR * V4 * kConsumerWarps * 32) + 15) & ~uintptr_t(15));
+        (reinterpret_cast<uintptr_t>(slots + (size_t)FR * V4 * kConsumerThreads) + 15) & ~uintptr_t(15));
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], kConsumerWarps); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&sm->sfull[b], kBwdScalarWarps); mbar_init(&sm->sempty[b], kConsumerWarps); }
+        for (int s = 0; s < NS; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], NCW); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm->sfull[b], kBwdScalarWarps); mbar_init(&sm->sempty[b], NCW); }
         sm->abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == kConsumerWarps + 1) {
+    if (warp == NCW + 1) {
         float m = 0.f;
         for (int i = lane; i < kMaxSources; i += 32) {
             float c = i < n ? p.c0[i] : 0.f;
@@ -88,21 +89,23 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         m = group_sum(m, 32);
         if (lane == 0) sm->mass = m;
     }
-    if (warp < kConsumerWarps) {
+    if (warp < NCW) {
 #pragma unroll
-        for (int k = 0; k < FR * V4; ++k) slots[(size_t)k * kConsumerWarps * 32 + threadIdx.x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < FR * V4; ++k) slots[(size_t)k * kConsumerThreads + threadIdx.x] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     __syncthreads();
     const WaitCtx wc{&sm->abort_flag, p.err_word};
     const long long n_tiles = p.tok_tiles;
     const int items_per_tile = 1 + n + (p.accum ? n : 0);
+    // stage layout: token-major [t][chunk][512 B] when one 4-D TMA box fills a stage, chunk-major [chunk][t][512 B]
+    // when the row is fetched chunk by chunk
+    const int tstride = p.rank4 ? p.chunks : 1, cstride = p.rank4 ? 1 : BT;
 
-    if (warp < kConsumerWarps) {
+    if (warp < NCW) {
         // ------------------------------------------------------------------ consumers
         const int t = warp / WPT;                 // token of the tile
         const int part = warp - t * WPT;          // which slice of the row
         const int chunk0 = part * FR;
-        const int row0 = chunk0 * BT + t;         // stage row of fragment k: row0 + k * BT
         const float mass = sm->mass, inv = p.inv_sqrt_d;
         const int bar_id = 1 + t, bar_threads = WPT * 32;
         long long it = 0;
@@ -112,8 +115,12 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         // storing, so every barrier still gets all its arrivals.
         bool alive = true;
         bool valid[FR];
+        int foff[FR];                             // byte offset of this lane's fragment k inside a stage
 #pragma unroll
-        for (int k = 0; k < FR; ++k) valid[k] = chunk0 + k < p.chunks;
+        for (int k = 0; k < FR; ++k) {
+            valid[k] = chunk0 + k < p.chunks;
+            foff[k] = ((t * tstride + (chunk0 + k) * cstride) * 32 + lane) * 16;
+        }
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
             const long long tok = tile * BT + t;
@@ -122,14 +129,14 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             const float *tb = tables + (size_t)buf * kBwdTables * tfl;
             const float *tP = tb, *tR = tb + tfl, *tGT = tb + 2 * tfl, *tW = tb + 3 * tfl, *tZL = tb + 4 * tfl,
                         *tDRP = tb + 5 * tfl;
-            // ---- g tile -> registers
-            uint4 gu[FR];
+            // ---- g tile -> registers (as fp32 pairs)
+            float2 g2[FR][P];
             {
                 const int st = (int)(it % NS);
                 if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
                 const uint8_t *sb = stages + (size_t)st * kStageBytes;
 #pragma unroll
-                for (int k = 0; k < FR; ++k) gu[k] = valid[k] ? ld_shared_v4(sb + ((size_t)(row0 + k * BT) * 32 + lane) * 16) : zero4;
+                for (int k = 0; k < FR; ++k) S::unpack2(valid[k] ? ld_shared_v4(sb + foff[k]) : zero4, g2[k]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->empty[st]);
                 ++it;
@@ -137,40 +144,40 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             if (alive && !mbar_wait(&sm->sfull[buf], (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
 
             // ---- phase 1: one pass over the sources, the accumulation of source i-1 overlapping the dot of i
-            float A[FR][VEC], B[FR][VEC];
+            float2 A[FR][P], B[FR][P];
+            uint4 vprev[FR];                      // the previous source's fragments, still packed
 #pragma unroll
-            for (int k = 0; k < FR; ++k)
+            for (int k = 0; k < FR; ++k) {
+                vprev[k] = zero4;
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) { A[k][e] = 0.f; B[k][e] = 0.f; }
+                for (int e = 0; e < P; ++e) { A[k][e] = make_float2(0.f, 0.f); B[k][e] = make_float2(0.f, 0.f); }
+            }
             float sacc = 0.f, dot_prev = 0.f;
-            uint4 vprev[FR];
-#pragma unroll
-            for (int k = 0; k < FR; ++k) vprev[k] = make_uint4(0, 0, 0, 0);
             for (int i = 0; i <= n; ++i) {
-                uint4 vcur[FR];
+                uint4 raw[FR];
                 float dot = 0.f;
                 if (i < n) {
                     const int st = (int)(it % NS);
                     if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
                     const uint8_t *sb = stages + (size_t)st * kStageBytes;
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) vcur[k] = valid[k] ? ld_shared_v4(sb + ((size_t)(row0 + k * BT) * 32 + lane) * 16) : zero4;
+                    for (int k = 0; k < FR; ++k) raw[k] = valid[k] ? ld_shared_v4(sb + foff[k]) : zero4;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->empty[st]);
                     ++it;
+                    float2 d2 = make_float2(0.f, 0.f);
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
-                        float gf[VEC], vf[VEC];
-                        S::unpack(gu[k], gf);
-                        S::unpack(vcur[k], vf);
+                        float2 vf[P];
+                        S::unpack2(raw[k], vf);
 #pragma unroll
-                        for (int e = 0; e < VEC; ++e) dot = fmaf(gf[e], vf[e], dot);
+                        for (int e = 0; e < P; ++e) d2 = __ffma2_rn(g2[k][e], vf[e], d2);
                     }
-                    dot = warp_sum(dot);
+                    dot = warp_sum(d2.x + d2.y);
                     if (WPT > 1 && lane == 0) sm->xch[i & 1][warp] = dot;
                 } else {
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) vcur[k] = make_uint4(0, 0, 0, 0);
+                    for (int k = 0; k < FR; ++k) raw[k] = zero4;
                 }
                 if (i > 0) {
                     const int j = i - 1;
@@ -184,34 +191,38 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     const float gp = mass * (gd + tGT[j * BT + t]);
                     sacc = fmaf(pj, gp, sacc);
                     const float b = pj * rj, a = b * gp;
+                    const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
-                        float vf[VEC];
-                        S::unpack(vprev[k], vf);
+                        float2 vf[P];
+                        S::unpack2(vprev[k], vf);
 #pragma unroll
-                        for (int e = 0; e < VEC; ++e) { A[k][e] = fmaf(a, vf[e], A[k][e]); B[k][e] = fmaf(b, vf[e], B[k][e]); }
+                        for (int e = 0; e < P; ++e) {
+                            A[k][e] = __ffma2_rn(a2, vf[e], A[k][e]);
+                            B[k][e] = __ffma2_rn(b2, vf[e], B[k][e]);
+                        }
                     }
                 }
                 if (WPT > 1) named_bar_sync(bar_id, bar_threads);
                 dot_prev = dot;
 #pragma unroll
-                for (int k = 0; k < FR; ++k) vprev[k] = vcur[k];
+                for (int k = 0; k < FR; ++k) vprev[k] = raw[k];
             }
             // ---- query-gradient partial of this thread's columns: private shared-memory slots
+            if (alive && tok_in) {
+                const float2 ms2 = make_float2(-sacc, -sacc);
 #pragma unroll
-            for (int k = 0; k < FR; ++k)
+                for (int k = 0; k < FR; ++k)
 #pragma unroll
-                for (int e4 = 0; e4 < V4; ++e4) {
-                    float4 *sp = &slots[(size_t)(k * V4 + e4) * kConsumerWarps * 32 + threadIdx.x];
-                    float4 s4 = *sp;
-                    if (alive && tok_in) {
-                        s4.x += A[k][4 * e4 + 0] - sacc * B[k][4 * e4 + 0];
-                        s4.y += A[k][4 * e4 + 1] - sacc * B[k][4 * e4 + 1];
-                        s4.z += A[k][4 * e4 + 2] - sacc * B[k][4 * e4 + 2];
-                        s4.w += A[k][4 * e4 + 3] - sacc * B[k][4 * e4 + 3];
+                    for (int e4 = 0; e4 < V4; ++e4) {
+                        float4 *sp = &slots[(size_t)(k * V4 + e4) * kConsumerThreads + threadIdx.x];
+                        float4 s4 = *sp;
+                        const float2 lo = __ffma2_rn(ms2, B[k][2 * e4], A[k][2 * e4]);
+                        const float2 hi = __ffma2_rn(ms2, B[k][2 * e4 + 1], A[k][2 * e4 + 1]);
+                        s4.x += lo.x; s4.y += lo.y; s4.z += hi.x; s4.w += hi.y;
+                        *sp = s4;
                     }
-                    *sp = s4;
-                }
+            }
             // ---- per-source scalars of this token: lanes over sources, by the token's first warp
             __syncwarp();
             if (part == 0) {
@@ -230,7 +241,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             if (WPT > 1) named_bar_sync(bar_id, bar_threads); else __syncwarp();
 
             // ---- phase 2: the gradient of every source
-            float qf[FR][VEC];
+            float2 q2[FR][P];
 #pragma unroll
             for (int k = 0; k < FR; ++k) {
                 const int col = (chunk0 + k) * BW + lane * VEC;
@@ -238,38 +249,34 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 for (int e4 = 0; e4 < V4; ++e4) {
                     float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (col < p.d) q4 = __ldg(reinterpret_cast<const float4 *>(p.q + col) + e4);
-                    qf[k][4 * e4] = q4.x; qf[k][4 * e4 + 1] = q4.y; qf[k][4 * e4 + 2] = q4.z; qf[k][4 * e4 + 3] = q4.w;
+                    q2[k][2 * e4] = make_float2(q4.x, q4.y);
+                    q2[k][2 * e4 + 1] = make_float2(q4.z, q4.w);
                 }
             }
             T *dvbase = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d;
             const long long src_stride = p.n_tok * (long long)p.d;
             for (int i = 0; i < n; ++i) {
                 const float wi = tW[i * BT + t], kq = gdkq[i * BT + t];
+                const float2 w2 = make_float2(wi, wi), kq2 = make_float2(kq, kq);
                 uint4 prev[FR];
                 if (p.accum) {
                     const int st = (int)(it % NS);
                     if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
                     const uint8_t *sb = stages + (size_t)st * kStageBytes;
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? ld_shared_v4(sb + ((size_t)(row0 + k * BT) * 32 + lane) * 16) : zero4;
+                    for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? ld_shared_v4(sb + foff[k]) : zero4;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->empty[st]);
                     ++it;
                 }
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
-                    float gf[VEC], o[VEC];
-                    S::unpack(gu[k], gf);
+                    float2 o[P];
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) o[e] = fmaf(wi, gf[e], kq * qf[k][e]);
-                    if (p.accum) {
-                        float pf[VEC];
-                        S::unpack(prev[k], pf);
-#pragma unroll
-                        for (int e = 0; e < VEC; ++e) o[e] = pf[e] + S::round(o[e]);
-                    }
+                    for (int e = 0; e < P; ++e) o[e] = __ffma2_rn(w2, g2[k][e], __fmul2_rn(kq2, q2[k][e]));
+                    const uint4 res = p.accum ? S::accum(prev[k], o) : S::pack2v(o);
                     const int col = (chunk0 + k) * BW + lane * VEC;
-                    if (alive && tok_in && col < p.d) st_global_v4(dvbase + (long long)i * src_stride + col, S::pack(o));
+                    if (alive && tok_in && col < p.d) st_global_v4(dvbase + (long long)i * src_stride + col, res);
                 }
             }
             // the token's warps leave the tile together: gdkq and xch are reused by the next tile
@@ -277,7 +284,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             if (lane == 0) mbar_arrive(&sm->sempty[buf]);
         }
         // ---- the CTA's query-gradient row: sum the private slots over the tile's tokens
-        named_bar_sync(15, kConsumerWarps * 32);
+        named_bar_sync(15, kConsumerThreads);
         if (t == 0) {
 #pragma unroll
             for (int k = 0; k < FR; ++k) {
@@ -286,7 +293,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 for (int e4 = 0; e4 < V4; ++e4) {
                     float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int t2 = 0; t2 < BT; ++t2) {
-                        const float4 v4 = slots[(size_t)(k * V4 + e4) * kConsumerWarps * 32 + (t2 * WPT + part) * 32 + lane];
+                        const float4 v4 = slots[(size_t)(k * V4 + e4) * kConsumerThreads + (t2 * WPT + part) * 32 + lane];
                         s4.x += v4.x; s4.y += v4.y; s4.z += v4.z; s4.w += v4.w;
                     }
                     if (col < p.d)
@@ -294,7 +301,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 }
             }
         }
-    } else if (warp == kConsumerWarps) {
+    } else if (warp == NCW) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             tma_prefetch_desc(&tmV);
@@ -313,11 +320,17 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     }
                     uint8_t *sb = stages + (size_t)st * kStageBytes;
                     mbar_arrive_expect_tx(&sm->full[st], (uint32_t)(nch * BT * kChunkBytes));
-                    for (int c = 0; c < nch; ++c) {
-                        uint8_t *dst = sb + (size_t)c * BT * kChunkBytes;
-                        if (item == 0) tma_load_2d(dst, &tmG, &sm->full[st], c * BW, tok0);
-                        else if (item <= n) tma_load_3d(dst, &tmV, &sm->full[st], c * BW, tok0, item - 1);
-                        else tma_load_3d(dst, &tmDV, &sm->full[st], c * BW, tok0, item - 1 - n);
+                    if (p.rank4) {
+                        if (item == 0) tma_load_3d(sb, &tmG, &sm->full[st], 0, 0, tok0);
+                        else if (item <= n) tma_load_4d(sb, &tmV, &sm->full[st], 0, 0, tok0, item - 1);
+                        else tma_load_4d(sb, &tmDV, &sm->full[st], 0, 0, tok0, item - 1 - n);
+                    } else {
+                        for (int c = 0; c < nch; ++c) {
+                            uint8_t *dst = sb + (size_t)c * BT * kChunkBytes;
+                            if (item == 0) tma_load_2d(dst, &tmG, &sm->full[st], c * BW, tok0);
+                            else if (item <= n) tma_load_3d(dst, &tmV, &sm->full[st], c * BW, tok0, item - 1);
+                            else tma_load_3d(dst, &tmDV, &sm->full[st], c * BW, tok0, item - 1 - n);
+                        }
                     }
                 }
             }
@@ -334,7 +347,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------------ scalar warps: tables of the next tile
-        const int sw = warp - kConsumerWarps - 1;
+        const int sw = warp - NCW - 1;
         const float mass = sm->mass;
         int tcount = 0;
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
@@ -368,26 +381,29 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     }
 }
 
-template <typename T, int FR>
+template <typename T, int FR, int NCW>
 static cudaError_t launch_bwd(const CUtensorMap &tmV, const CUtensorMap &tmG, const CUtensorMap &tmDV,
                               const ReadBwdParams &p, int grid, cudaStream_t stream) {
-    size_t smem = read_bwd_smem_bytes(FR, p.wpt, p.stages, p.n, Store<T>::kVec);
-    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    size_t smem = read_bwd_smem_bytes(FR, NCW, p.wpt, p.stages, p.n, Store<T>::kVec);
+    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR, NCW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    read_bwd_kernel<T, FR><<<grid, kBwdThreads, smem, stream>>>(tmV, tmG, tmDV, p);
+    read_bwd_kernel<T, FR, NCW><<<grid, (NCW + 1 + kBwdScalarWarps) * 32, smem, stream>>>(tmV, tmG, tmDV, p);
     return cudaGetLastError();
 }
 
-cudaError_t launch_read_bwd(int dtype, int fr, const CUtensorMap &tmV, const CUtensorMap &tmG,
+cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmG,
                             const CUtensorMap &tmDV, const ReadBwdParams &p, int grid, cudaStream_t stream) {
-#define LB_BWD_CASE(TT, F) return launch_bwd<TT, F>(tmV, tmG, tmDV, p, grid, stream)
+#define LB_BWD_CASE(TT, F, W) return launch_bwd<TT, F, W>(tmV, tmG, tmDV, p, grid, stream)
+#define LB_BWD_FR(TT, W) \
+    switch (fr) { case 1: LB_BWD_CASE(TT, 1, W); case 2: LB_BWD_CASE(TT, 2, W); case 3: LB_BWD_CASE(TT, 3, W); default: break; }
     if (dtype == LB_DTYPE_BF16) {
-        switch (fr) { case 1: LB_BWD_CASE(__nv_bfloat16, 1); case 2: LB_BWD_CASE(__nv_bfloat16, 2);
-                      case 3: LB_BWD_CASE(__nv_bfloat16, 3); case 4: LB_BWD_CASE(__nv_bfloat16, 4); }
+        if (ncw == 16) { LB_BWD_FR(__nv_bfloat16, 16) }
+        else if (ncw == 8) { LB_BWD_FR(__nv_bfloat16, 8) if (fr == 4) LB_BWD_CASE(__nv_bfloat16, 4, 8); }
     } else {
-        switch (fr) { case 1: LB_BWD_CASE(float, 1); case 2: LB_BWD_CASE(float, 2);
-                      case 3: LB_BWD_CASE(float, 3); case 4: LB_BWD_CASE(float, 4); }
+        if (ncw == 16) { LB_BWD_FR(float, 16) }
+        else if (ncw == 8) { LB_BWD_FR(float, 8) if (fr == 4) LB_BWD_CASE(float, 4, 8); }
     }
+#undef LB_BWD_FR
 #undef LB_BWD_CASE
     return cudaErrorInvalidValue;
 }

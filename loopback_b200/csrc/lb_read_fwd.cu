@@ -6,24 +6,25 @@
 // Replaces the reference's stored-score read kernel (fused_dattn.py:588-625) and the host preparation around it
 // (fused_dattn.py:735-745: log-prior and mass are formed in the kernel from c0).
 //
-// One persistent CTA per SM slot walks tiles of 8 tokens x FR chunks (a chunk is 512 B of a row). Warp roles:
-//   warps 0..7   consumers: warp w owns token w of the tile; lane l owns fragment l of each chunk; fp32 accumulators
-//   warp  8      producer: one lane issues TMA tile loads (base tile, then V[0..n) tiles) into a ring of stages
-//   warps 9..10  scalar warps: per tile, the n-source softmaxes of the 8 tokens -> coefficient table in shared
-//                memory (double buffered, one tile ahead of the consumers), and the saved TC / LG / LSE / LSE0
+// One persistent CTA per SM walks tiles of NCW tokens x FR chunks (a chunk is 512 B of a row; NCW = 8 or 16).
+// Warp roles:
+//   NCW consumers  warp w owns token w of the tile; lane l owns fragment l of each chunk; fp32 accumulators held as
+//                  pairs (fma.rn.f32x2)
+//   1 producer     one lane issues TMA tile loads (base tile, then V[0..n) tiles) into a ring of stages
+//   4 scalar warps per tile, the n-source softmaxes of its tokens -> coefficient table in shared memory (double
+//                  buffered, one tile ahead of the consumers), and the saved TC / LG / LSE / LSE0
 // Every wait is bounded (see lb_common.cuh); nothing here spins forever or traps.
 #include "lb_common.cuh"
 #include "lb_kernels.h"
 
 namespace lb {
 
-constexpr int kFwdBT = 8;                         // tokens per tile == consumer warps
-constexpr int kFwdScalarWarps = 2;
-constexpr int kFwdThreads = (kConsumerWarps + 1 + kFwdScalarWarps) * 32;
+constexpr int kFwdScalarWarps = 4;
 constexpr int kFwdMaxStages = 12;
+constexpr int kFwdMaxBT = 16;                     // tokens per tile == consumer warps (8 or 16)
 
 struct FwdSmemTail {
-    float wtab[2][kMaxSources * kFwdBT];          // coefficient deltas w[i][t], double buffered by tile
+    float wtab[2][kMaxSources * kFwdMaxBT];       // coefficient deltas w[i][t], double buffered by tile
     float c0[kMaxSources];
     float lc[kMaxSources];
     float mass;
@@ -34,16 +35,19 @@ struct FwdSmemTail {
     uint64_t sempty[2];
 };
 
-size_t read_fwd_smem_bytes(int fr, int stages) {
-    return 1024 + (size_t)stages * (size_t)fr * kFwdBT * kChunkBytes + sizeof(FwdSmemTail);
+size_t read_fwd_smem_bytes(int fr, int ncw, int stages) {
+    return 1024 + (size_t)stages * (size_t)fr * ncw * kChunkBytes + sizeof(FwdSmemTail);
 }
 
-template <typename T, int FR>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+template <typename T, int FR, int NCW>
+__global__ void __launch_bounds__((NCW + 1 + kFwdScalarWarps) * 32, 1)
 read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBase, ReadFwdParams p) {
     using S = Store<T>;
     constexpr int VEC = S::kVec;
+    constexpr int P = S::kPairs;
     constexpr int BW = kChunkBytes / S::kBytes;               // columns per chunk
+    constexpr int kFwdBT = NCW;                                // one consumer warp per token of the tile
+    constexpr int kConsumerWarps = NCW;
     constexpr int kStageBytes = FR * kFwdBT * kChunkBytes;
 
     extern __shared__ uint8_t smem_raw[];
@@ -81,22 +85,23 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         long long it = 0;
         int tcount = 0;
         bool alive = true;      // turned off by a wait that ran out: the warp then finishes its loops without waiting or storing
+        int foff[FR];           // byte offset of this lane's fragment k inside a stage (token-major if one 4-D box fills it)
+#pragma unroll
+        for (int k = 0; k < FR; ++k)
+            foff[k] = ((p.rank4 ? warp * FR + k : k * kFwdBT + warp) * 32 + lane) * 16;
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
             const long long tt = tile / cg_count;
             const int cg = (int)(tile - tt * cg_count);
             const long long tok = tt * kFwdBT + warp;
             const int chunk0 = cg * FR;
             const int buf = tcount & 1;
-            float acc[FR][VEC];
+            float2 acc[FR][P];
             {   // item 0: the base tile
                 const int st = (int)(it % NS);
                 if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
                 const uint8_t *sb = stages + (size_t)st * kStageBytes;
 #pragma unroll
-                for (int k = 0; k < FR; ++k) {
-                    uint4 u = ld_shared_v4(sb + ((size_t)(k * kFwdBT + warp) * 32 + lane) * 16);
-                    S::unpack(u, acc[k]);
-                }
+                for (int k = 0; k < FR; ++k) S::unpack2(ld_shared_v4(sb + foff[k]), acc[k]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->empty[st]);
                 ++it;
@@ -108,17 +113,18 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
                 const uint8_t *sb = stages + (size_t)st * kStageBytes;
                 const float wi = wt[i * kFwdBT + warp];
+                const float2 w2 = make_float2(wi, wi);
                 uint4 u[FR];
 #pragma unroll
-                for (int k = 0; k < FR; ++k) u[k] = ld_shared_v4(sb + ((size_t)(k * kFwdBT + warp) * 32 + lane) * 16);
+                for (int k = 0; k < FR; ++k) u[k] = ld_shared_v4(sb + foff[k]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->empty[st]);
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
-                    float v[VEC];
-                    S::unpack(u[k], v);
+                    float2 v[P];
+                    S::unpack2(u[k], v);
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) acc[k][e] = fmaf(wi, v[e], acc[k][e]);
+                    for (int e = 0; e < P; ++e) acc[k][e] = __ffma2_rn(w2, v[e], acc[k][e]);
                 }
             }
             __syncwarp();
@@ -128,7 +134,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
                     const int col = (chunk0 + k) * BW + lane * VEC;
-                    if (col < p.d) st_global_v4(orow + col, S::pack(acc[k]));
+                    if (col < p.d) st_global_v4(orow + col, S::pack2v(acc[k]));
                 }
             }
         }
@@ -152,6 +158,12 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                         break;
                     }
                     uint8_t *sb = stages + (size_t)st * kStageBytes;
+                    if (p.rank4) {          // one box: FR chunks x BT tokens (chunks past the row are zero-filled)
+                        mbar_arrive_expect_tx(&sm->full[st], (uint32_t)kStageBytes);
+                        if (item < 0) tma_load_3d(sb, &tmBase, &sm->full[st], 0, chunk0, tok0);
+                        else tma_load_4d(sb, &tmV, &sm->full[st], 0, chunk0, tok0, item);
+                        continue;
+                    }
                     mbar_arrive_expect_tx(&sm->full[st], (uint32_t)(nch * kFwdBT * kChunkBytes));
                     for (int c = 0; c < nch; ++c) {
                         if (item < 0)
@@ -247,26 +259,28 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     }
 }
 
-template <typename T, int FR>
+template <typename T, int FR, int NCW>
 static cudaError_t launch_fwd(const CUtensorMap &tmV, const CUtensorMap &tmBase, const ReadFwdParams &p, int grid,
                               cudaStream_t stream) {
-    size_t smem = read_fwd_smem_bytes(FR, p.stages);
-    cudaError_t e = cudaFuncSetAttribute(read_fwd_kernel<T, FR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    size_t smem = read_fwd_smem_bytes(FR, NCW, p.stages);
+    cudaError_t e = cudaFuncSetAttribute(read_fwd_kernel<T, FR, NCW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    read_fwd_kernel<T, FR><<<grid, kFwdThreads, smem, stream>>>(tmV, tmBase, p);
+    read_fwd_kernel<T, FR, NCW><<<grid, (NCW + 1 + kFwdScalarWarps) * 32, smem, stream>>>(tmV, tmBase, p);
     return cudaGetLastError();
 }
 
-cudaError_t launch_read_fwd(int dtype, int fr, const CUtensorMap &tmV, const CUtensorMap &tmBase,
+cudaError_t launch_read_fwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmBase,
                             const ReadFwdParams &p, int grid, cudaStream_t stream) {
-#define LB_FWD_CASE(TT, F) return launch_fwd<TT, F>(tmV, tmBase, p, grid, stream)
+#define LB_FWD_CASE(TT, F, W) return launch_fwd<TT, F, W>(tmV, tmBase, p, grid, stream)
+#define LB_FWD_FR(TT, W) \
+    switch (fr) { case 1: LB_FWD_CASE(TT, 1, W); case 2: LB_FWD_CASE(TT, 2, W); case 3: LB_FWD_CASE(TT, 3, W); \
+                  case 4: LB_FWD_CASE(TT, 4, W); default: break; }
     if (dtype == LB_DTYPE_BF16) {
-        switch (fr) { case 1: LB_FWD_CASE(__nv_bfloat16, 1); case 2: LB_FWD_CASE(__nv_bfloat16, 2);
-                      case 3: LB_FWD_CASE(__nv_bfloat16, 3); case 4: LB_FWD_CASE(__nv_bfloat16, 4); }
+        if (ncw == 16) { LB_FWD_FR(__nv_bfloat16, 16) } else if (ncw == 8) { LB_FWD_FR(__nv_bfloat16, 8) }
     } else {
-        switch (fr) { case 1: LB_FWD_CASE(float, 1); case 2: LB_FWD_CASE(float, 2);
-                      case 3: LB_FWD_CASE(float, 3); case 4: LB_FWD_CASE(float, 4); }
+        if (ncw == 16) { LB_FWD_FR(float, 16) } else if (ncw == 8) { LB_FWD_FR(float, 8) }
     }
+#undef LB_FWD_FR
 #undef LB_FWD_CASE
     return cudaErrorInvalidValue;
 }
