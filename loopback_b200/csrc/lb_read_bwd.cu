@@ -108,7 +108,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         const int chunk0 = part * FR;
         const float mass = sm->mass, inv = p.inv_sqrt_d;
         const int bar_id = 1 + t, bar_threads = WPT * 32;
-        long long it = 0;
+        int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
         int tcount = 0;
         // A wait that runs out must not make this warp leave: its sibling warps meet it at named barriers. It
         // turns `alive` off instead, and the warp walks the remaining (finite) loop structure without waiting or
@@ -132,14 +132,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             // ---- g tile -> registers (as fp32 pairs)
             float2 g2[FR][P];
             {
-                const int st = (int)(it % NS);
-                if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
                 const uint8_t *sb = stages + (size_t)st * kStageBytes;
 #pragma unroll
                 for (int k = 0; k < FR; ++k) S::unpack2(valid[k] ? ld_shared_v4(sb + foff[k]) : zero4, g2[k]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->empty[st]);
-                ++it;
+                if (++st == NS) { st = 0; ph ^= 1u; }
             }
             if (alive && !mbar_wait(&sm->sfull[buf], (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
 
@@ -157,14 +156,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 uint4 raw[FR];
                 float dot = 0.f;
                 if (i < n) {
-                    const int st = (int)(it % NS);
-                    if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                        if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
                     const uint8_t *sb = stages + (size_t)st * kStageBytes;
 #pragma unroll
                     for (int k = 0; k < FR; ++k) raw[k] = valid[k] ? ld_shared_v4(sb + foff[k]) : zero4;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->empty[st]);
-                    ++it;
+                    if (++st == NS) { st = 0; ph ^= 1u; }
                     float2 d2 = make_float2(0.f, 0.f);
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
@@ -260,14 +258,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 const float2 w2 = make_float2(wi, wi), kq2 = make_float2(kq, kq);
                 uint4 prev[FR];
                 if (p.accum) {
-                    const int st = (int)(it % NS);
-                    if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                        if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
                     const uint8_t *sb = stages + (size_t)st * kStageBytes;
 #pragma unroll
                     for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? ld_shared_v4(sb + foff[k]) : zero4;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->empty[st]);
-                    ++it;
+                    if (++st == NS) { st = 0; ph ^= 1u; }
                 }
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
@@ -307,14 +304,14 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             tma_prefetch_desc(&tmV);
             tma_prefetch_desc(&tmG);
             if (p.accum) tma_prefetch_desc(&tmDV);
-            long long it = 0;
+            int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
+            int issued = 0;
             bool ok = true;
             const int nch = p.chunks;                       // the full row
             for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const int tok0 = (int)(tile * BT);
-                for (int item = 0; item < items_per_tile; ++item, ++it) {
-                    const int st = (int)(it % NS);
-                    if (!mbar_wait(&sm->empty[st], (uint32_t)(((it / NS) & 1) ^ 1), wc, kDevWaitEmpty)) {
+                for (int item = 0; item < items_per_tile; ++item) {
+                        if (!mbar_wait(&sm->empty[st], ph ^ 1u, wc, kDevWaitEmpty)) {
                         ok = false;
                         break;
                     }
@@ -332,14 +329,17 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                             else tma_load_3d(dst, &tmDV, &sm->full[st], c * BW, tok0, item - 1 - n);
                         }
                     }
+                    ++issued;
+                    if (++st == NS) { st = 0; ph ^= 1u; }
                 }
             }
             if (!ok) {
-                const long long first = it > NS ? it - NS : 0;
+                // the last min(issued, NS) fills, walking the ring backwards from the current position
                 long long t0 = clock64();
-                for (long long f = first; f < it; ++f) {
-                    const int st = (int)(f % NS);
-                    while (!mbar_try_wait(&sm->full[st], (uint32_t)((f / NS) & 1))) {
+                int ds = st; uint32_t dp = ph;
+                for (int k = 0; k < NS && k < issued; ++k) {
+                    if (--ds < 0) { ds = NS - 1; dp ^= 1u; }
+                    while (!mbar_try_wait(&sm->full[ds], dp)) {
                         if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
                     }
                 }

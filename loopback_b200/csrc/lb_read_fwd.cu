@@ -82,7 +82,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 
     if (warp < kConsumerWarps) {
         // ------------------------------------------------------------------ consumers
-        long long it = 0;
+        int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
         int tcount = 0;
         bool alive = true;      // turned off by a wait that ran out: the warp then finishes its loops without waiting or storing
         int foff[FR];           // byte offset of this lane's fragment k inside a stage (token-major if one 4-D box fills it)
@@ -97,20 +97,18 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             const int buf = tcount & 1;
             float2 acc[FR][P];
             {   // item 0: the base tile
-                const int st = (int)(it % NS);
-                if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+                if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
                 const uint8_t *sb = stages + (size_t)st * kStageBytes;
 #pragma unroll
                 for (int k = 0; k < FR; ++k) S::unpack2(ld_shared_v4(sb + foff[k]), acc[k]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->empty[st]);
-                ++it;
+                if (++st == NS) { st = 0; ph ^= 1u; }
             }
             if (alive && !mbar_wait(&sm->sfull[buf], (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
             const float *wt = sm->wtab[buf];
-            for (int i = 0; i < n; ++i, ++it) {
-                const int st = (int)(it % NS);
-                if (alive && !mbar_wait(&sm->full[st], (uint32_t)((it / NS) & 1), wc, kDevWaitFull)) alive = false;
+            for (int i = 0; i < n; ++i) {
+                if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
                 const uint8_t *sb = stages + (size_t)st * kStageBytes;
                 const float wi = wt[i * kFwdBT + warp];
                 const float2 w2 = make_float2(wi, wi);
@@ -119,6 +117,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 for (int k = 0; k < FR; ++k) u[k] = ld_shared_v4(sb + foff[k]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->empty[st]);
+                if (++st == NS) { st = 0; ph ^= 1u; }
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
                     float2 v[P];
@@ -143,7 +142,8 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         if (lane == 0) {
             tma_prefetch_desc(&tmV);
             tma_prefetch_desc(&tmBase);
-            long long it = 0;
+            int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
+            int issued = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const long long tt = tile / cg_count;
@@ -151,9 +151,8 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 const int tok0 = (int)(tt * kFwdBT);
                 const int chunk0 = cg * FR;
                 const int nch = min(FR, p.chunks - chunk0);
-                for (int item = -1; item < n; ++item, ++it) {
-                    const int st = (int)(it % NS);
-                    if (!mbar_wait(&sm->empty[st], (uint32_t)(((it / NS) & 1) ^ 1), wc, kDevWaitEmpty)) {
+                for (int item = -1; item < n; ++item) {
+                    if (!mbar_wait(&sm->empty[st], ph ^ 1u, wc, kDevWaitEmpty)) {
                         ok = false;
                         break;
                     }
@@ -162,26 +161,29 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                         mbar_arrive_expect_tx(&sm->full[st], (uint32_t)kStageBytes);
                         if (item < 0) tma_load_3d(sb, &tmBase, &sm->full[st], 0, chunk0, tok0);
                         else tma_load_4d(sb, &tmV, &sm->full[st], 0, chunk0, tok0, item);
-                        continue;
+                    } else {
+                        mbar_arrive_expect_tx(&sm->full[st], (uint32_t)(nch * kFwdBT * kChunkBytes));
+                        for (int c = 0; c < nch; ++c) {
+                            if (item < 0)
+                                tma_load_2d(sb + (size_t)c * kFwdBT * kChunkBytes, &tmBase, &sm->full[st],
+                                            (chunk0 + c) * BW, tok0);
+                            else
+                                tma_load_3d(sb + (size_t)c * kFwdBT * kChunkBytes, &tmV, &sm->full[st],
+                                            (chunk0 + c) * BW, tok0, item);
+                        }
                     }
-                    mbar_arrive_expect_tx(&sm->full[st], (uint32_t)(nch * kFwdBT * kChunkBytes));
-                    for (int c = 0; c < nch; ++c) {
-                        if (item < 0)
-                            tma_load_2d(sb + (size_t)c * kFwdBT * kChunkBytes, &tmBase, &sm->full[st],
-                                        (chunk0 + c) * BW, tok0);
-                        else
-                            tma_load_3d(sb + (size_t)c * kFwdBT * kChunkBytes, &tmV, &sm->full[st],
-                                        (chunk0 + c) * BW, tok0, item);
-                    }
+                    ++issued;
+                    if (++st == NS) { st = 0; ph ^= 1u; }
                 }
             }
             if (!ok) {
                 // unwinding: let the copies already issued land before the CTA's shared memory is released
-                const long long first = it > NS ? it - NS : 0;
+                // the last min(issued, NS) fills, walking the ring backwards from the current position
                 long long t0 = clock64();
-                for (long long f = first; f < it; ++f) {
-                    const int st = (int)(f % NS);
-                    while (!mbar_try_wait(&sm->full[st], (uint32_t)((f / NS) & 1))) {
+                int ds = st; uint32_t dp = ph;
+                for (int k = 0; k < NS && k < issued; ++k) {
+                    if (--ds < 0) { ds = NS - 1; dp ^= 1u; }
+                    while (!mbar_try_wait(&sm->full[ds], dp)) {
                         if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
                     }
                 }
