@@ -16,6 +16,8 @@
 // Tiles are BT = NCW / WPT tokens x the full row; a token's row is split over WPT consumer warps (FR chunks of
 // 512 B each). Warp roles: NCW consumer warps, 1 TMA producer lane, 2 scalar warps that prepare the
 // per-(token, source) tables of the next tile. The element math runs on pairs (fma.rn.f32x2). All waits are bounded.
+#include <cstddef>
+
 #include "lb_common.cuh"
 #include "lb_kernels.h"
 
@@ -38,7 +40,7 @@ struct BwdSmemTail {
     uint64_t sempty[2];
 };
 
-// dynamic shared memory: [stages][tables 2 x 6 x n_pad*BT][gdkq n_pad*BT][dq slots][tail]
+// dynamic shared memory: [stages][tables 2 x 6 x n_pad*BT][gdkq n_pad*BT][dq slots][q: chunks*512/elem floats][tail]
 __host__ __device__ inline int bwd_npad(int n) { return (n + 3) & ~3; }
 __host__ __device__ inline size_t bwd_table_floats(int n, int bt) { return (size_t)bwd_npad(n) * bt; }
 
@@ -46,7 +48,8 @@ size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec)
     size_t stage = (size_t)fr * ncw * kChunkBytes;
     size_t tables = (2 * kBwdTables + 1) * bwd_table_floats(n, ncw / wpt) * sizeof(float);
     size_t slots = (size_t)fr * vec * sizeof(float) * ncw * 32;
-    return 1024 + stages * stage + ((tables + 15) & ~size_t(15)) + slots + sizeof(BwdSmemTail) + 64;
+    size_t qrow = (size_t)fr * wpt * 32 * vec * sizeof(float);       // the query, padded to whole chunks
+    return 1024 + stages * stage + ((tables + 15) & ~size_t(15)) + slots + qrow + sizeof(BwdSmemTail) + 64;
 }
 
 template <typename T, int FR, int NCW>
@@ -58,43 +61,54 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     constexpr int P = S::kPairs;
     constexpr int V4 = VEC / 4;
     constexpr int BW = kChunkBytes / S::kBytes;
-    constexpr int kStageBytes = FR * NCW * kChunkBytes;
+    constexpr uint32_t kStageBytes = FR * NCW * kChunkBytes;
     constexpr int kConsumerThreads = NCW * 32;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NS = p.stages, n = p.n, WPT = p.wpt, BT = NCW / WPT;
-    const size_t tfl = bwd_table_floats(n, BT);
+    const uint32_t tfl4 = (uint32_t)bwd_table_floats(n, BT) * 4u;      // bytes of one table
 
+    // shared-window addresses of the regions of the dynamic shared memory
     extern __shared__ uint8_t smem_raw[];
-    uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    float *tables = reinterpret_cast<float *>(stages + (size_t)NS * kStageBytes);
-    float *gdkq = tables + 2 * kBwdTables * tfl;
-    float4 *slots = reinterpret_cast<float4 *>((reinterpret_cast<uintptr_t>(gdkq + tfl) + 15) & ~uintptr_t(15));
-    BwdSmemTail *sm = reinterpret_cast<BwdSmemTail *>(
-        (reinterpret_cast<uintptr_t>(slots + (size_t)FR * V4 * kConsumerThreads) + 15) & ~uintptr_t(15));
+    const uint32_t stages_a = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t tables_a = stages_a + (uint32_t)NS * kStageBytes;
+    const uint32_t gdkq_a = tables_a + 2u * kBwdTables * tfl4;
+    const uint32_t slots_a = (gdkq_a + tfl4 + 15u) & ~15u;
+    const uint32_t qsm_a = slots_a + (uint32_t)(FR * V4 * kConsumerThreads) * 16u;
+    const uint32_t tail_a = (qsm_a + (uint32_t)(FR * WPT * 32 * V4) * 16u + 15u) & ~15u;
+    const uint32_t c0_a = tail_a + offsetof(BwdSmemTail, c0), lc_a = tail_a + offsetof(BwdSmemTail, lc);
+    const uint32_t mass_a = tail_a + offsetof(BwdSmemTail, mass), abort_a = tail_a + offsetof(BwdSmemTail, abort_flag);
+    const uint32_t xch_a = tail_a + offsetof(BwdSmemTail, xch);
+    const uint32_t full_a = tail_a + offsetof(BwdSmemTail, full), empty_a = tail_a + offsetof(BwdSmemTail, empty);
+    const uint32_t sfull_a = tail_a + offsetof(BwdSmemTail, sfull), sempty_a = tail_a + offsetof(BwdSmemTail, sempty);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], NCW); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&sm->sfull[b], kBwdScalarWarps); mbar_init(&sm->sempty[b], NCW); }
-        sm->abort_flag = 0;
+        for (int s = 0; s < NS; ++s) { mbar_init(full_a + 8u * s, 1); mbar_init(empty_a + 8u * s, NCW); }
+        for (int b = 0; b < 2; ++b) { mbar_init(sfull_a + 8u * b, kBwdScalarWarps); mbar_init(sempty_a + 8u * b, NCW); }
+        sts_s32(abort_a, 0);
         fence_mbar_init();
     }
     if (warp == NCW + 1) {
         float m = 0.f;
         for (int i = lane; i < kMaxSources; i += 32) {
             float c = i < n ? p.c0[i] : 0.f;
-            if (i < n) { sm->c0[i] = c; sm->lc[i] = logf(fmaxf(c, 1e-8f)); }
+            if (i < n) { sts_f32(c0_a + 4u * i, c); sts_f32(lc_a + 4u * i, logf(fmaxf(c, 1e-8f))); }
             m += c;
         }
         m = group_sum(m, 32);
-        if (lane == 0) sm->mass = m;
+        if (lane == 0) sts_f32(mass_a, m);
     }
     if (warp < NCW) {
 #pragma unroll
-        for (int k = 0; k < FR * V4; ++k) slots[(size_t)k * kConsumerThreads + threadIdx.x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < FR * V4; ++k)
+            sts_f4(slots_a + (uint32_t)(k * kConsumerThreads + threadIdx.x) * 16u, make_float4(0.f, 0.f, 0.f, 0.f));
+        // the query stays in shared memory for the whole kernel: no global load sits in the consumers' path
+        for (int f4 = threadIdx.x; f4 < FR * WPT * 32 * V4; f4 += kConsumerThreads)
+            sts_f4(qsm_a + 16u * f4, f4 * 4 < p.d ? __ldg(reinterpret_cast<const float4 *>(p.q) + f4)
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f));
     }
     __syncthreads();
-    const WaitCtx wc{&sm->abort_flag, p.err_word};
+    const WaitCtx wc{abort_a, p.err_word};
     const long long n_tiles = p.tok_tiles;
     const int items_per_tile = 1 + n + (p.accum ? n : 0);
     // stage layout: token-major [t][chunk][512 B] when one 4-D TMA box fills a stage, chunk-major [chunk][t][512 B]
@@ -106,41 +120,42 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         const int t = warp / WPT;                 // token of the tile
         const int part = warp - t * WPT;          // which slice of the row
         const int chunk0 = part * FR;
-        const float mass = sm->mass, inv = p.inv_sqrt_d;
+        const float mass = lds_f32(mass_a), inv = p.inv_sqrt_d;
         const int bar_id = 1 + t, bar_threads = WPT * 32;
-        int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
+        const uint32_t BT4 = 4u * BT, t4 = 4u * t;
+        int st = 0; uint32_t ph = 0;              // ring position: stage index and its phase parity
         int tcount = 0;
         // A wait that runs out must not make this warp leave: its sibling warps meet it at named barriers. It
         // turns `alive` off instead, and the warp walks the remaining (finite) loop structure without waiting or
         // storing, so every barrier still gets all its arrivals.
         bool alive = true;
         bool valid[FR];
-        int foff[FR];                             // byte offset of this lane's fragment k inside a stage
+        uint32_t foff[FR];                        // byte offset of this lane's fragment k inside a stage
 #pragma unroll
         for (int k = 0; k < FR; ++k) {
             valid[k] = chunk0 + k < p.chunks;
-            foff[k] = ((t * tstride + (chunk0 + k) * cstride) * 32 + lane) * 16;
+            foff[k] = (uint32_t)((t * tstride + (chunk0 + k) * cstride) * 32 + lane) * 16u;
         }
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
             const long long tok = tile * BT + t;
             const bool tok_in = tok < p.n_tok;
-            const int buf = tcount & 1;
-            const float *tb = tables + (size_t)buf * kBwdTables * tfl;
-            const float *tP = tb, *tR = tb + tfl, *tGT = tb + 2 * tfl, *tW = tb + 3 * tfl, *tZL = tb + 4 * tfl,
-                        *tDRP = tb + 5 * tfl;
+            const uint32_t buf = tcount & 1;
+            // tables of this tile, entry (i, t) of table k at tb + k * tfl4 + i * BT4 + t4:  P, R, GT, W, ZL, DRP
+            const uint32_t tb = tables_a + buf * kBwdTables * tfl4 + t4;
+            const uint32_t gk = gdkq_a + t4;
             // ---- g tile -> registers (as fp32 pairs)
             float2 g2[FR][P];
             {
-                if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
-                const uint8_t *sb = stages + (size_t)st * kStageBytes;
+                if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
 #pragma unroll
-                for (int k = 0; k < FR; ++k) S::unpack2(valid[k] ? ld_shared_v4(sb + foff[k]) : zero4, g2[k]);
+                for (int k = 0; k < FR; ++k) S::unpack2(valid[k] ? lds_v4(sb + foff[k]) : zero4, g2[k]);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->empty[st]);
+                if (lane == 0) mbar_arrive(empty_a + 8u * st);
                 if (++st == NS) { st = 0; ph ^= 1u; }
             }
-            if (alive && !mbar_wait(&sm->sfull[buf], (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
+            if (alive && !mbar_wait(sfull_a + 8u * buf, (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
 
             // ---- phase 1: one pass over the sources, the accumulation of source i-1 overlapping the dot of i
             float2 A[FR][P], B[FR][P];
@@ -156,37 +171,41 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 uint4 raw[FR];
                 float dot = 0.f;
                 if (i < n) {
-                        if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
-                    const uint8_t *sb = stages + (size_t)st * kStageBytes;
+                    if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                    const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) raw[k] = valid[k] ? ld_shared_v4(sb + foff[k]) : zero4;
+                    for (int k = 0; k < FR; ++k) raw[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sm->empty[st]);
+                    if (lane == 0) mbar_arrive(empty_a + 8u * st);
                     if (++st == NS) { st = 0; ph ^= 1u; }
-                    float2 d2 = make_float2(0.f, 0.f);
+                    float2 d2a = make_float2(0.f, 0.f), d2b = make_float2(0.f, 0.f);
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
                         float2 vf[P];
                         S::unpack2(raw[k], vf);
 #pragma unroll
-                        for (int e = 0; e < P; ++e) d2 = __ffma2_rn(g2[k][e], vf[e], d2);
+                        for (int e = 0; e < P; e += 2) {
+                            d2a = __ffma2_rn(g2[k][e], vf[e], d2a);
+                            d2b = __ffma2_rn(g2[k][e + 1], vf[e + 1], d2b);
+                        }
                     }
-                    dot = warp_sum(d2.x + d2.y);
-                    if (WPT > 1 && lane == 0) sm->xch[i & 1][warp] = dot;
+                    dot = warp_sum((d2a.x + d2b.x) + (d2a.y + d2b.y));
+                    if (WPT > 1 && lane == 0) sts_f32(xch_a + 4u * ((i & 1) * kBwdMaxNcw + warp), dot);
                 } else {
 #pragma unroll
                     for (int k = 0; k < FR; ++k) raw[k] = zero4;
                 }
                 if (i > 0) {
-                    const int j = i - 1;
+                    const uint32_t j4 = (uint32_t)(i - 1) * BT4;
                     float gd = dot_prev;
                     if (WPT > 1) {
                         gd = 0.f;
-                        for (int w2 = 0; w2 < WPT; ++w2) gd += sm->xch[j & 1][t * WPT + w2];
+                        const uint32_t xa = xch_a + 4u * (((i - 1) & 1) * kBwdMaxNcw + t * WPT);
+                        for (int w2 = 0; w2 < WPT; ++w2) gd += lds_f32(xa + 4u * w2);
                     }
-                    if (part == 0 && lane == 0) gdkq[j * BT + t] = gd;
-                    const float pj = tP[j * BT + t], rj = tR[j * BT + t];
-                    const float gp = mass * (gd + tGT[j * BT + t]);
+                    if (part == 0 && lane == 0) sts_f32(gk + j4, gd);
+                    const float pj = lds_f32(tb + j4), rj = lds_f32(tb + tfl4 + j4);
+                    const float gp = mass * (gd + lds_f32(tb + 2u * tfl4 + j4));
                     sacc = fmaf(pj, gp, sacc);
                     const float b = pj * rj, a = b * gp;
                     const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
@@ -213,25 +232,26 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 for (int k = 0; k < FR; ++k)
 #pragma unroll
                     for (int e4 = 0; e4 < V4; ++e4) {
-                        float4 *sp = &slots[(size_t)(k * V4 + e4) * kConsumerThreads + threadIdx.x];
-                        float4 s4 = *sp;
+                        const uint32_t sa = slots_a + (uint32_t)((k * V4 + e4) * kConsumerThreads + threadIdx.x) * 16u;
+                        float4 s4 = lds_f4(sa);
                         const float2 lo = __ffma2_rn(ms2, B[k][2 * e4], A[k][2 * e4]);
                         const float2 hi = __ffma2_rn(ms2, B[k][2 * e4 + 1], A[k][2 * e4 + 1]);
                         s4.x += lo.x; s4.y += lo.y; s4.z += hi.x; s4.w += hi.y;
-                        *sp = s4;
+                        sts_f4(sa, s4);
                     }
             }
             // ---- per-source scalars of this token: lanes over sources, by the token's first warp
             __syncwarp();
             if (part == 0) {
                 for (int i = lane; i < n; i += 32) {
-                    const float gd = gdkq[i * BT + t];
-                    const float pi = tP[i * BT + t], ri = tR[i * BT + t];
-                    const float gp = mass * (gd + tGT[i * BT + t]);
+                    const uint32_t i4 = (uint32_t)i * BT4;
+                    const float gd = lds_f32(gk + i4);
+                    const float pi = lds_f32(tb + i4), ri = lds_f32(tb + tfl4 + i4);
+                    const float gp = mass * (gd + lds_f32(tb + 2u * tfl4 + i4));
                     const float dz = pi * (gp - sacc);
-                    gdkq[i * BT + t] = dz * ri * inv;
+                    sts_f32(gk + i4, dz * ri * inv);
                     if (alive && tok_in) {
-                        p.dR[(long long)i * p.n_tok + tok] = tDRP[i * BT + t] + dz * tZL[i * BT + t];
+                        p.dR[(long long)i * p.n_tok + tok] = lds_f32(tb + 5u * tfl4 + i4) + dz * lds_f32(tb + 4u * tfl4 + i4);
                         p.dcbar[tok * n + i] = -gd;
                     }
                 }
@@ -245,25 +265,25 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 const int col = (chunk0 + k) * BW + lane * VEC;
 #pragma unroll
                 for (int e4 = 0; e4 < V4; ++e4) {
-                    float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (col < p.d) q4 = __ldg(reinterpret_cast<const float4 *>(p.q + col) + e4);
+                    const float4 q4 = lds_f4(qsm_a + 16u * (col / 4 + e4));
                     q2[k][2 * e4] = make_float2(q4.x, q4.y);
                     q2[k][2 * e4 + 1] = make_float2(q4.z, q4.w);
                 }
             }
-            T *dvbase = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d;
+            T *dvrow = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d + chunk0 * BW + lane * VEC;
             const long long src_stride = p.n_tok * (long long)p.d;
             for (int i = 0; i < n; ++i) {
-                const float wi = tW[i * BT + t], kq = gdkq[i * BT + t];
+                const uint32_t i4 = (uint32_t)i * BT4;
+                const float wi = lds_f32(tb + 3u * tfl4 + i4), kq = lds_f32(gk + i4);
                 const float2 w2 = make_float2(wi, wi), kq2 = make_float2(kq, kq);
                 uint4 prev[FR];
                 if (p.accum) {
-                        if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
-                    const uint8_t *sb = stages + (size_t)st * kStageBytes;
+                    if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                    const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? ld_shared_v4(sb + foff[k]) : zero4;
+                    for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sm->empty[st]);
+                    if (lane == 0) mbar_arrive(empty_a + 8u * st);
                     if (++st == NS) { st = 0; ph ^= 1u; }
                 }
 #pragma unroll
@@ -273,12 +293,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     for (int e = 0; e < P; ++e) o[e] = __ffma2_rn(w2, g2[k][e], __fmul2_rn(kq2, q2[k][e]));
                     const uint4 res = p.accum ? S::accum(prev[k], o) : S::pack2v(o);
                     const int col = (chunk0 + k) * BW + lane * VEC;
-                    if (alive && tok_in && col < p.d) st_global_v4(dvbase + (long long)i * src_stride + col, res);
+                    if (alive && tok_in && col < p.d) st_global_v4(dvrow + k * BW, res);
                 }
+                dvrow += src_stride;
             }
             // the token's warps leave the tile together: gdkq and xch are reused by the next tile
             if (WPT > 1) named_bar_sync(bar_id, bar_threads); else __syncwarp();
-            if (lane == 0) mbar_arrive(&sm->sempty[buf]);
+            if (lane == 0) mbar_arrive(sempty_a + 8u * buf);
         }
         // ---- the CTA's query-gradient row: sum the private slots over the tile's tokens
         named_bar_sync(15, kConsumerThreads);
@@ -290,7 +311,8 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 for (int e4 = 0; e4 < V4; ++e4) {
                     float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int t2 = 0; t2 < BT; ++t2) {
-                        const float4 v4 = slots[(size_t)(k * V4 + e4) * kConsumerThreads + (t2 * WPT + part) * 32 + lane];
+                        const float4 v4 = lds_f4(slots_a + (uint32_t)((k * V4 + e4) * kConsumerThreads +
+                                                                      (t2 * WPT + part) * 32 + lane) * 16u);
                         s4.x += v4.x; s4.y += v4.y; s4.z += v4.z; s4.w += v4.w;
                     }
                     if (col < p.d)
@@ -304,29 +326,29 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             tma_prefetch_desc(&tmV);
             tma_prefetch_desc(&tmG);
             if (p.accum) tma_prefetch_desc(&tmDV);
-            int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
+            int st = 0; uint32_t ph = 0;
             int issued = 0;
             bool ok = true;
             const int nch = p.chunks;                       // the full row
             for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const int tok0 = (int)(tile * BT);
                 for (int item = 0; item < items_per_tile; ++item) {
-                        if (!mbar_wait(&sm->empty[st], ph ^ 1u, wc, kDevWaitEmpty)) {
+                    if (!mbar_wait(empty_a + 8u * st, ph ^ 1u, wc, kDevWaitEmpty)) {
                         ok = false;
                         break;
                     }
-                    uint8_t *sb = stages + (size_t)st * kStageBytes;
-                    mbar_arrive_expect_tx(&sm->full[st], (uint32_t)(nch * BT * kChunkBytes));
+                    const uint32_t sb = stages_a + (uint32_t)st * kStageBytes, fb = full_a + 8u * st;
+                    mbar_arrive_expect_tx(fb, (uint32_t)(nch * BT * kChunkBytes));
                     if (p.rank4) {
-                        if (item == 0) tma_load_3d(sb, &tmG, &sm->full[st], 0, 0, tok0);
-                        else if (item <= n) tma_load_4d(sb, &tmV, &sm->full[st], 0, 0, tok0, item - 1);
-                        else tma_load_4d(sb, &tmDV, &sm->full[st], 0, 0, tok0, item - 1 - n);
+                        if (item == 0) tma_load_3d(sb, &tmG, fb, 0, 0, tok0);
+                        else if (item <= n) tma_load_4d(sb, &tmV, fb, 0, 0, tok0, item - 1);
+                        else tma_load_4d(sb, &tmDV, fb, 0, 0, tok0, item - 1 - n);
                     } else {
                         for (int c = 0; c < nch; ++c) {
-                            uint8_t *dst = sb + (size_t)c * BT * kChunkBytes;
-                            if (item == 0) tma_load_2d(dst, &tmG, &sm->full[st], c * BW, tok0);
-                            else if (item <= n) tma_load_3d(dst, &tmV, &sm->full[st], c * BW, tok0, item - 1);
-                            else tma_load_3d(dst, &tmDV, &sm->full[st], c * BW, tok0, item - 1 - n);
+                            const uint32_t dst = sb + (uint32_t)(c * BT * kChunkBytes);
+                            if (item == 0) tma_load_2d(dst, &tmG, fb, c * BW, tok0);
+                            else if (item <= n) tma_load_3d(dst, &tmV, fb, c * BW, tok0, item - 1);
+                            else tma_load_3d(dst, &tmDV, fb, c * BW, tok0, item - 1 - n);
                         }
                     }
                     ++issued;
@@ -334,12 +356,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 }
             }
             if (!ok) {
+                // unwinding: let the copies already issued land before the CTA's shared memory is released --
                 // the last min(issued, NS) fills, walking the ring backwards from the current position
                 long long t0 = clock64();
                 int ds = st; uint32_t dp = ph;
                 for (int k = 0; k < NS && k < issued; ++k) {
                     if (--ds < 0) { ds = NS - 1; dp ^= 1u; }
-                    while (!mbar_try_wait(&sm->full[ds], dp)) {
+                    while (!mbar_try_wait(full_a + 8u * ds, dp)) {
                         if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
                     }
                 }
@@ -348,13 +371,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     } else {
         // ------------------------------------------------------------------ scalar warps: tables of the next tile
         const int sw = warp - NCW - 1;
-        const float mass = sm->mass;
+        const float mass = lds_f32(mass_a);
         int tcount = 0;
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
-            const int buf = tcount & 1;
-            if (!mbar_wait(&sm->sempty[buf], (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
+            const uint32_t buf = tcount & 1;
+            if (!mbar_wait(sempty_a + 8u * buf, (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
                 return;
-            float *tb = tables + (size_t)buf * kBwdTables * tfl;
+            const uint32_t tb = tables_a + buf * kBwdTables * tfl4;
             for (int idx = sw * 32 + lane; idx < BT * n; idx += kBwdScalarWarps * 32) {
                 const int t = idx / n, i = idx - t * n;
                 long long tok = tile * BT + t;
@@ -365,18 +388,18 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 const float gtv = p.gt ? __ldg(p.gt + tok * n + i) : 0.f;
                 const float r = __ldg(p.R + (long long)i * p.n_tok + tok);
                 const float drp = p.accum ? p.dR[(long long)i * p.n_tok + tok] : 0.f;
-                const float lci = sm->lc[i];
+                const float lci = lds_f32(lc_a + 4u * i);
                 const float pi = expf(lg - lse), p0 = expf(lci - lse0);
-                const int o = i * BT + t;
-                tb[o] = pi;
-                tb[tfl + o] = r;
-                tb[2 * tfl + o] = gtv;
-                tb[3 * tfl + o] = sm->c0[i] - cb + mass * (pi - p0);
-                tb[4 * tfl + o] = (lg - lci) / r;
-                tb[5 * tfl + o] = drp;
+                const uint32_t o = tb + 4u * (uint32_t)(i * BT + t);
+                sts_f32(o, pi);
+                sts_f32(o + tfl4, r);
+                sts_f32(o + 2u * tfl4, gtv);
+                sts_f32(o + 3u * tfl4, lds_f32(c0_a + 4u * i) - cb + mass * (pi - p0));
+                sts_f32(o + 4u * tfl4, (lg - lci) / r);
+                sts_f32(o + 5u * tfl4, drp);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm->sfull[buf]);
+            if (lane == 0) mbar_arrive(sfull_a + 8u * buf);
         }
     }
 }

@@ -14,6 +14,8 @@
 //   4 scalar warps per tile, the n-source softmaxes of its tokens -> coefficient table in shared memory (double
 //                  buffered, one tile ahead of the consumers), and the saved TC / LG / LSE / LSE0
 // Every wait is bounded (see lb_common.cuh); nothing here spins forever or traps.
+#include <cstddef>
+
 #include "lb_common.cuh"
 #include "lb_kernels.h"
 
@@ -46,77 +48,85 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     constexpr int VEC = S::kVec;
     constexpr int P = S::kPairs;
     constexpr int BW = kChunkBytes / S::kBytes;               // columns per chunk
-    constexpr int kFwdBT = NCW;                                // one consumer warp per token of the tile
-    constexpr int kConsumerWarps = NCW;
-    constexpr int kStageBytes = FR * kFwdBT * kChunkBytes;
+    constexpr int BT = NCW;                                    // one consumer warp per token of the tile
+    constexpr uint32_t kStageBytes = FR * BT * kChunkBytes;
 
+    // shared-window addresses of the regions of the dynamic shared memory
     extern __shared__ uint8_t smem_raw[];
-    uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    FwdSmemTail *sm = reinterpret_cast<FwdSmemTail *>(stages + (size_t)p.stages * kStageBytes);
+    const uint32_t stages_a = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t tail_a = stages_a + (uint32_t)p.stages * kStageBytes;
+    const uint32_t wtab_a = tail_a + offsetof(FwdSmemTail, wtab);
+    const uint32_t c0_a = tail_a + offsetof(FwdSmemTail, c0), lc_a = tail_a + offsetof(FwdSmemTail, lc);
+    const uint32_t mass_a = tail_a + offsetof(FwdSmemTail, mass), abort_a = tail_a + offsetof(FwdSmemTail, abort_flag);
+    const uint32_t full_a = tail_a + offsetof(FwdSmemTail, full), empty_a = tail_a + offsetof(FwdSmemTail, empty);
+    const uint32_t sfull_a = tail_a + offsetof(FwdSmemTail, sfull), sempty_a = tail_a + offsetof(FwdSmemTail, sempty);
+    constexpr uint32_t kWtabBytes = kMaxSources * kFwdMaxBT * 4;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NS = p.stages;
     const int n = p.n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], kConsumerWarps); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&sm->sfull[b], kFwdScalarWarps); mbar_init(&sm->sempty[b], kConsumerWarps); }
-        sm->abort_flag = 0;
+        for (int s = 0; s < NS; ++s) { mbar_init(full_a + 8u * s, 1); mbar_init(empty_a + 8u * s, NCW); }
+        for (int b = 0; b < 2; ++b) { mbar_init(sfull_a + 8u * b, kFwdScalarWarps); mbar_init(sempty_a + 8u * b, NCW); }
+        sts_s32(abort_a, 0);
         fence_mbar_init();
     }
-    if (warp == kConsumerWarps + 1) {           // prior tables: c0, log-prior, mass
+    if (warp == NCW + 1) {           // prior tables: c0, log-prior, mass
         float m = 0.f;
         for (int i = lane; i < kMaxSources; i += 32) {
             float c = i < n ? p.c0[i] : 0.f;
-            if (i < n) { sm->c0[i] = c; sm->lc[i] = logf(fmaxf(c, 1e-8f)); }
+            if (i < n) { sts_f32(c0_a + 4u * i, c); sts_f32(lc_a + 4u * i, logf(fmaxf(c, 1e-8f))); }
             m += c;
         }
         m = group_sum(m, 32);
-        if (lane == 0) sm->mass = m;
+        if (lane == 0) sts_f32(mass_a, m);
     }
     __syncthreads();
-    const WaitCtx wc{&sm->abort_flag, p.err_word};
+    const WaitCtx wc{abort_a, p.err_word};
 
     const int cg_count = p.col_groups;
     const long long n_tiles = (long long)p.tok_tiles * cg_count;
 
-    if (warp < kConsumerWarps) {
+    if (warp < NCW) {
         // ------------------------------------------------------------------ consumers
         int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
         int tcount = 0;
         bool alive = true;      // turned off by a wait that ran out: the warp then finishes its loops without waiting or storing
-        int foff[FR];           // byte offset of this lane's fragment k inside a stage (token-major if one 4-D box fills it)
+        uint32_t foff[FR];      // byte offset of this lane's fragment k inside a stage (token-major if one 4-D box fills it)
 #pragma unroll
         for (int k = 0; k < FR; ++k)
-            foff[k] = ((p.rank4 ? warp * FR + k : k * kFwdBT + warp) * 32 + lane) * 16;
+            foff[k] = (uint32_t)((p.rank4 ? warp * FR + k : k * BT + warp) * 32 + lane) * 16u;
+        long long tt = blockIdx.x / cg_count;
+        int cg = (int)(blockIdx.x - tt * cg_count);
+        const long long tt_step = gridDim.x / cg_count;
+        const int cg_step = (int)(gridDim.x - tt_step * cg_count);
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
-            const long long tt = tile / cg_count;
-            const int cg = (int)(tile - tt * cg_count);
-            const long long tok = tt * kFwdBT + warp;
+            const long long tok = tt * BT + warp;
             const int chunk0 = cg * FR;
-            const int buf = tcount & 1;
+            const uint32_t buf = tcount & 1;
             float2 acc[FR][P];
             {   // item 0: the base tile
-                if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
-                const uint8_t *sb = stages + (size_t)st * kStageBytes;
+                if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
 #pragma unroll
-                for (int k = 0; k < FR; ++k) S::unpack2(ld_shared_v4(sb + foff[k]), acc[k]);
+                for (int k = 0; k < FR; ++k) S::unpack2(lds_v4(sb + foff[k]), acc[k]);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->empty[st]);
+                if (lane == 0) mbar_arrive(empty_a + 8u * st);
                 if (++st == NS) { st = 0; ph ^= 1u; }
             }
-            if (alive && !mbar_wait(&sm->sfull[buf], (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
-            const float *wt = sm->wtab[buf];
-            for (int i = 0; i < n; ++i) {
-                if (alive && !mbar_wait(&sm->full[st], ph, wc, kDevWaitFull)) alive = false;
-                const uint8_t *sb = stages + (size_t)st * kStageBytes;
-                const float wi = wt[i * kFwdBT + warp];
+            if (alive && !mbar_wait(sfull_a + 8u * buf, (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
+            uint32_t wa = wtab_a + buf * kWtabBytes + 4u * warp;
+            for (int i = 0; i < n; ++i, wa += 4u * BT) {
+                if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+                const float wi = lds_f32(wa);
                 const float2 w2 = make_float2(wi, wi);
                 uint4 u[FR];
 #pragma unroll
-                for (int k = 0; k < FR; ++k) u[k] = ld_shared_v4(sb + foff[k]);
+                for (int k = 0; k < FR; ++k) u[k] = lds_v4(sb + foff[k]);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->empty[st]);
+                if (lane == 0) mbar_arrive(empty_a + 8u * st);
                 if (++st == NS) { st = 0; ph ^= 1u; }
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
@@ -127,7 +137,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm->sempty[buf]);
+            if (lane == 0) mbar_arrive(sempty_a + 8u * buf);
             if (alive && tok < p.n_tok) {
                 T *orow = reinterpret_cast<T *>(p.out) + tok * (long long)p.d;
 #pragma unroll
@@ -136,40 +146,39 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     if (col < p.d) st_global_v4(orow + col, S::pack2v(acc[k]));
                 }
             }
+            tt += tt_step; cg += cg_step;
+            if (cg >= cg_count) { cg -= cg_count; ++tt; }
         }
-    } else if (warp == kConsumerWarps) {
+    } else if (warp == NCW) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             tma_prefetch_desc(&tmV);
             tma_prefetch_desc(&tmBase);
-            int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
+            int st = 0; uint32_t ph = 0;
             int issued = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const long long tt = tile / cg_count;
                 const int cg = (int)(tile - tt * cg_count);
-                const int tok0 = (int)(tt * kFwdBT);
+                const int tok0 = (int)(tt * BT);
                 const int chunk0 = cg * FR;
                 const int nch = min(FR, p.chunks - chunk0);
                 for (int item = -1; item < n; ++item) {
-                    if (!mbar_wait(&sm->empty[st], ph ^ 1u, wc, kDevWaitEmpty)) {
+                    if (!mbar_wait(empty_a + 8u * st, ph ^ 1u, wc, kDevWaitEmpty)) {
                         ok = false;
                         break;
                     }
-                    uint8_t *sb = stages + (size_t)st * kStageBytes;
+                    const uint32_t sb = stages_a + (uint32_t)st * kStageBytes, fb = full_a + 8u * st;
                     if (p.rank4) {          // one box: FR chunks x BT tokens (chunks past the row are zero-filled)
-                        mbar_arrive_expect_tx(&sm->full[st], (uint32_t)kStageBytes);
-                        if (item < 0) tma_load_3d(sb, &tmBase, &sm->full[st], 0, chunk0, tok0);
-                        else tma_load_4d(sb, &tmV, &sm->full[st], 0, chunk0, tok0, item);
+                        mbar_arrive_expect_tx(fb, kStageBytes);
+                        if (item < 0) tma_load_3d(sb, &tmBase, fb, 0, chunk0, tok0);
+                        else tma_load_4d(sb, &tmV, fb, 0, chunk0, tok0, item);
                     } else {
-                        mbar_arrive_expect_tx(&sm->full[st], (uint32_t)(nch * kFwdBT * kChunkBytes));
+                        mbar_arrive_expect_tx(fb, (uint32_t)(nch * BT * kChunkBytes));
                         for (int c = 0; c < nch; ++c) {
-                            if (item < 0)
-                                tma_load_2d(sb + (size_t)c * kFwdBT * kChunkBytes, &tmBase, &sm->full[st],
-                                            (chunk0 + c) * BW, tok0);
-                            else
-                                tma_load_3d(sb + (size_t)c * kFwdBT * kChunkBytes, &tmV, &sm->full[st],
-                                            (chunk0 + c) * BW, tok0, item);
+                            const uint32_t dst = sb + (uint32_t)(c * BT * kChunkBytes);
+                            if (item < 0) tma_load_2d(dst, &tmBase, fb, (chunk0 + c) * BW, tok0);
+                            else tma_load_3d(dst, &tmV, fb, (chunk0 + c) * BW, tok0, item);
                         }
                     }
                     ++issued;
@@ -177,13 +186,13 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 }
             }
             if (!ok) {
-                // unwinding: let the copies already issued land before the CTA's shared memory is released
+                // unwinding: let the copies already issued land before the CTA's shared memory is released --
                 // the last min(issued, NS) fills, walking the ring backwards from the current position
                 long long t0 = clock64();
                 int ds = st; uint32_t dp = ph;
                 for (int k = 0; k < NS && k < issued; ++k) {
                     if (--ds < 0) { ds = NS - 1; dp ^= 1u; }
-                    while (!mbar_try_wait(&sm->full[ds], dp)) {
+                    while (!mbar_try_wait(full_a + 8u * ds, dp)) {
                         if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
                     }
                 }
@@ -191,22 +200,22 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------------ scalar warps
-        const int sw = warp - kConsumerWarps - 1;
+        const int sw = warp - NCW - 1;
         const int G = n >= 32 ? 32 : (n <= 2 ? 2 : (n <= 4 ? 4 : (n <= 8 ? 8 : (n <= 16 ? 16 : 32))));
         const int TPP = 32 / G;
         const int sub = lane / G, ii = lane % G;
-        const float inv = p.inv_sqrt_d, mass = sm->mass;
+        const float inv = p.inv_sqrt_d, mass = lds_f32(mass_a);
         int tcount = 0;
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
             const long long tt = tile / cg_count;
             const int cg = (int)(tile - tt * cg_count);
-            const int buf = tcount & 1;
-            if (!mbar_wait(&sm->sempty[buf], (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
+            const uint32_t buf = tcount & 1;
+            if (!mbar_wait(sempty_a + 8u * buf, (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
                 return;
-            float *wt = sm->wtab[buf];
-            for (int pass = sw; pass * TPP < kFwdBT; pass += kFwdScalarWarps) {
+            const uint32_t wt = wtab_a + buf * kWtabBytes;
+            for (int pass = sw; pass * TPP < BT; pass += kFwdScalarWarps) {
                 const int t = pass * TPP + sub;
-                const long long tok_raw = tt * kFwdBT + t;
+                const long long tok_raw = tt * BT + t;
                 const bool tok_ok = tok_raw < p.n_tok;
                 const long long tok = tok_ok ? tok_raw : p.n_tok - 1;
                 float l[kMaxSources / 32], lcv[kMaxSources / 32], cb[kMaxSources / 32];
@@ -219,7 +228,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                         const float r = __ldg(p.R + (long long)i * p.n_tok + tok);
                         const float dt = __ldg(p.dots + (long long)i * p.n_tok + tok);
                         cb[k] = __ldg(p.cbar + tok * n + i);
-                        lcv[k] = sm->lc[i];
+                        lcv[k] = lds_f32(lc_a + 4u * i);
                         l[k] = dt * r * inv + lcv[k];
                     }
                 }
@@ -242,21 +251,21 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 #pragma unroll
                 for (int k = 0; k < kMaxSources / 32; ++k) {
                     const int i = ii + 32 * k;
-                    const bool act = i < n && (k == 0 || G == 32);
+                    const bool act = i < n && (k == 0 || G == 32) && t < BT;
                     if (act) {
                         const float pi = expf(l[k] - lse), p0 = expf(lcv[k] - lse0);
-                        const float tc = sm->c0[i] + mass * (pi - p0);
-                        wt[i * kFwdBT + t] = tc - cb[k];
+                        const float tc = lds_f32(c0_a + 4u * i) + mass * (pi - p0);
+                        sts_f32(wt + 4u * (uint32_t)(i * BT + t), tc - cb[k]);
                         if (cg == 0 && tok_ok) {
                             p.TC[tok * n + i] = tc;
                             if (p.LG) p.LG[tok * n + i] = l[k];
                         }
                     }
                 }
-                if (ii == 0 && cg == 0 && tok_ok && p.LSE) { p.LSE[tok] = lse; p.LSE0[tok] = lse0; }
+                if (ii == 0 && cg == 0 && tok_ok && t < BT && p.LSE) { p.LSE[tok] = lse; p.LSE0[tok] = lse0; }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm->sfull[buf]);
+            if (lane == 0) mbar_arrive(sfull_a + 8u * buf);
         }
     }
 }
