@@ -115,6 +115,23 @@ int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float 
                 const float *cbar, const float *c0, const float *LG, const float *LSE, const float *LSE0, float *dcbar,
                 float *dq, void *scratch, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream);
 
+/* The widest row lb_read_bwd_noalloc accepts. */
+#define LB_NOALLOC_MAX_D 3072
+
+/* lb_read_bwd without the `scratch` argument, for callers that are not able to allocate device memory (a runtime
+ * that plans all its memory up front and forbids allocation afterwards, a plugin host that only passes the tensors
+ * of the current call). The partial rows of the query gradient go to a fixed array inside the library instead
+ * (about 3.6 MiB, resident on every GPU that uses the library, until the process exits). Arguments, results and
+ * rounding are exactly those of lb_read_bwd. It allocates nothing and calls no allocating routine.
+ * Limits: d <= LB_NOALLOC_MAX_D, otherwise LB_ERR_UNSUPPORTED; all calls on a device share the array, so calls that
+ * overlap in time on that GPU race (serialise them on one stream; nothing needs clearing between calls); the first
+ * call on a device resolves the array's device address and should be made outside any stream capture.
+ * This entry point has no counterpart in the reference. */
+int lb_read_bwd_noalloc(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
+                        const float *gt, const float *cbar, const float *c0, const float *LG, const float *LSE,
+                        const float *LSE0, float *dcbar, float *dq, int64_t n_tok, int d, int N, int n, int accum,
+                        int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

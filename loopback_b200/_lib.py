@@ -33,6 +33,8 @@ SYMBOLS = {
     "lb_read_bwd_scratch_bytes": (ctypes.c_size_t, [_i]),
     "lb_read_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
                          _i, _i, _vp]),
+    "lb_read_bwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
+                                 _i, _i, _vp]),
 }
 
 _lib = None

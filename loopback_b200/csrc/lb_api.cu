@@ -145,6 +145,9 @@ int chunks_of(int d, int dtype) {
 
 }  // namespace
 
+// sets the calling thread's error message from another translation unit of this library (not exported)
+extern "C" int lb_fail_message(int code, const char *msg) { return fail(code, "%s", msg); }
+
 #pragma GCC visibility push(default)
 extern "C" {
 
