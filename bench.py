@@ -283,7 +283,7 @@ def main():
     for kind, n, accum, a, b_ in launches:
         ms = a.elapsed_time(b_)
         if kind == "read_bwd":
-            units = n + (2 * n if accum else n) + 1            # V, dV (read+write or write), g
+            units = n + (2 * n if accum else n) + 2            # V, dV (read+write or write), g, dx = -dV[n-1]
         elif kind == "read_fwd":
             units = n + 2                                       # V, base, out
         else:
@@ -295,7 +295,7 @@ def main():
     if args.detail and rank == 0:
         rows = {}
         for kind, n, accum, a, b_ in launches:
-            units = (n + (2 * n if accum else n) + 1) if kind == "read_bwd" else ((n + 2) if kind == "read_fwd" else 3)
+            units = (n + (2 * n if accum else n) + 2) if kind == "read_bwd" else ((n + 2) if kind == "read_fwd" else 3)
             r = rows.setdefault((kind, n, bool(accum)), [0.0, 0, units])
             r[0] += a.elapsed_time(b_)
             r[1] += 1

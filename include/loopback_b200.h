@@ -115,6 +115,17 @@ int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float 
                 const float *cbar, const float *c0, const float *LG, const float *LSE, const float *LSE0, float *dcbar,
                 float *dq, void *scratch, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream);
 
+/* lb_read_bwd that also finishes the gradient of the newest source (index n - 1), for the read that is the last, in
+ * backward order, to touch it: after adding its own contribution it adds the term that reaches the update through
+ * its key scale, dV[n-1] = round(dV[n-1] + round(dR[n-1] * (-R[n-1]^3 / d) * V[n-1])) with the complete dR[n-1], and,
+ * if neg_out != NULL, writes -dV[n-1] ([n_tok][d], storage dtype) there: the gradient of the block input.
+ * Fuses _RstdStk.backward / _rstd_bwd_acc_kernel and _WriteDelta.backward into the read's backward
+ * (fused_dattn.py:539-552, :711-722, :693-695): same values, two passes over the update less. */
+int lb_read_bwd_final(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
+                      const float *gt, const float *cbar, const float *c0, const float *LG, const float *LSE,
+                      const float *LSE0, float *dcbar, float *dq, void *scratch, void *neg_out, int64_t n_tok, int d,
+                      int N, int n, int accum, int dtype, void *stream);
+
 /* The widest row lb_read_bwd_noalloc accepts. */
 #define LB_NOALLOC_MAX_D 3072
 

@@ -33,6 +33,8 @@ SYMBOLS = {
     "lb_read_bwd_scratch_bytes": (ctypes.c_size_t, [_i]),
     "lb_read_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
                          _i, _i, _vp]),
+    "lb_read_bwd_final": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i,
+                               _i, _i, _i, _vp]),
     "lb_read_bwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
                                  _i, _i, _vp]),
 }
@@ -78,7 +80,7 @@ def stream_ptr(device=None):
 # kernels launched through this binding since import (lb_read_bwd launches two: the backward and the reduction
 # of its query-gradient partials); read by the benchmark
 LAUNCHES = {"count": 0}
-_KERNELS_PER_CALL = {"read backward": 2}
+_KERNELS_PER_CALL = {"read backward": 2, "read backward (final)": 2}
 
 
 def check(rc: int, what: str) -> None:

@@ -331,9 +331,31 @@ int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const 
 
 size_t lb_read_bwd_scratch_bytes(int d) { return d > 0 ? (size_t)kMaxGrid * (size_t)d * sizeof(float) : 0; }
 
+static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
+                         const float *gt, const float *cbar, const float *c0, const float *LG, const float *LSE,
+                         const float *LSE0, float *dcbar, float *dq, void *scratch, int64_t n_tok, int d, int N, int n,
+                         int accum, int finalize, void *neg_out, int dtype, void *stream);
+
 int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
                 const float *cbar, const float *c0, const float *LG, const float *LSE, const float *LSE0, float *dcbar,
                 float *dq, void *scratch, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream) {
+    return read_bwd_impl(V, R, dV, dR, q, g, gt, cbar, c0, LG, LSE, LSE0, dcbar, dq, scratch, n_tok, d, N, n, accum, 0,
+                         nullptr, dtype, stream);
+}
+
+int lb_read_bwd_final(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
+                      const float *gt, const float *cbar, const float *c0, const float *LG, const float *LSE,
+                      const float *LSE0, float *dcbar, float *dq, void *scratch, void *neg_out, int64_t n_tok, int d,
+                      int N, int n, int accum, int dtype, void *stream) {
+    if (neg_out && !aligned16(neg_out)) return fail(LB_ERR_ALIGN, "lb_read_bwd_final: neg_out must be 16-byte aligned");
+    return read_bwd_impl(V, R, dV, dR, q, g, gt, cbar, c0, LG, LSE, LSE0, dcbar, dq, scratch, n_tok, d, N, n, accum, 1,
+                         neg_out, dtype, stream);
+}
+
+static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
+                         const float *gt, const float *cbar, const float *c0, const float *LG, const float *LSE,
+                         const float *LSE0, float *dcbar, float *dq, void *scratch, int64_t n_tok, int d, int N, int n,
+                         int accum, int finalize, void *neg_out, int dtype, void *stream) {
     int rc = check_common(n_tok, d, dtype);
     if (rc) return rc;
     if (!V || !R || !dV || !dR || !q || !g || !cbar || !c0 || !LG || !LSE || !LSE0 || !dcbar || !dq || !scratch)
@@ -353,18 +375,24 @@ int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float 
     const int nch = chunks_of(d, dtype);
     const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
     const bool rank4 = !g_opt.tma_per_chunk && (d * elem) % lb::kChunkBytes == 0;
-    const int ncw = g_opt.bwd_warps == 8 ? 8 : 16;
-    // warps per token / fragments per warp: no wasted fragments first, then 2 fragments per warp, then 3, then 1
-    const int fr_max = ncw == 16 ? 3 : 4;
-    int wpt = 0, fr = 0, best_cost = 1 << 30;
-    for (int w = 1; w <= ncw; w <<= 1) {
-        const int f = (nch + w - 1) / w;
-        if (f > fr_max) continue;
-        const int cost = (f * w - nch) * 8 + (f == 2 ? 0 : (f == 3 ? 1 : (f == 1 ? 2 : 3)));
-        if (g_opt.bwd_wpt == w) { wpt = w; fr = f; break; }
-        if (cost < best_cost) { best_cost = cost; wpt = w; fr = f; }
+    // consumer warps (16, 12 or 8), warps per token and fragments per warp: no idle fragments first, then tiles of
+    // at least 12 KiB, then 2 fragments per warp, then more warps
+    int ncw = 0, wpt = 0, fr = 0, best_cost = 1 << 30;
+    static const int kNcw[3] = {12, 16, 8}, kFrMax[3] = {2, 2, 4};
+    for (int a = 0; a < 3; ++a) {
+        if (g_opt.bwd_warps && g_opt.bwd_warps != kNcw[a]) continue;
+        for (int w = 1; w <= kNcw[a]; ++w) {
+            if (kNcw[a] % w) continue;
+            if (w > 1 && kNcw[a] / w > 8) continue;          // named barriers 1..8: one per token of the tile
+            if (g_opt.bwd_wpt && g_opt.bwd_wpt != w) continue;
+            const int f = (nch + w - 1) / w;
+            if (f > kFrMax[a]) continue;
+            const int stage = nch * (kNcw[a] / w) * lb::kChunkBytes;
+            const int cost = (f * w - nch) * 64 + (stage < 12 * 1024 ? 16 : 0) + (f == 2 ? 0 : (f == 3 ? 2 : (f == 1 ? 3 : 4))) * 2 + a;
+            if (cost < best_cost) { best_cost = cost; ncw = kNcw[a]; wpt = w; fr = f; }
+        }
     }
-    if (wpt == 0) return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: d=%d needs more than %d chunks per row", d, fr_max * ncw);
+    if (ncw == 0) return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: no tile shape covers d=%d (row of %d chunks)", d, nch);
     const int bt = ncw / wpt;
     const int vec = dtype == LB_DTYPE_BF16 ? 8 : 4;
     int stages = g_opt.bwd_stages > 0 ? g_opt.bwd_stages : 8;
@@ -382,7 +410,8 @@ int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float 
     p.R = R; p.dR = dR; p.dV = dV; p.q = q; p.gt = gt; p.cbar = cbar; p.c0 = c0; p.LSE = LSE; p.LSE0 = LSE0; p.LG = LG;
     p.dcbar = dcbar; p.dq_part = static_cast<float *>(scratch);
     p.n_tok = n_tok; p.tok_tiles = (n_tok + bt - 1) / bt; p.d = d; p.n = n; p.chunks = nch; p.wpt = wpt;
-    p.stages = stages; p.rank4 = rank4 ? 1 : 0; p.accum = accum ? 1 : 0; p.inv_sqrt_d = 1.0f / sqrtf((float)d);
+    p.stages = stages; p.rank4 = rank4 ? 1 : 0; p.accum = accum ? 1 : 0; p.finalize = finalize ? 1 : 0;
+    p.neg_out = finalize ? neg_out : nullptr; p.inv_sqrt_d = 1.0f / sqrtf((float)d);
     p.err_word = di.err_word;
     int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
     if (cap > kMaxGrid) cap = kMaxGrid;

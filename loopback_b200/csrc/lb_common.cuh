@@ -203,6 +203,9 @@ template <> struct Store<__nv_bfloat16> {
         const uint4 r = pack2v(o);
         return make_uint4(hadd(prev.x, r.x), hadd(prev.y, r.y), hadd(prev.z, r.z), hadd(prev.w, r.w));
     }
+    __device__ __forceinline__ static uint4 negate(const uint4 &u) {
+        return make_uint4(u.x ^ 0x80008000u, u.y ^ 0x80008000u, u.z ^ 0x80008000u, u.w ^ 0x80008000u);
+    }
 };
 
 template <> struct Store<float> {
@@ -234,6 +237,9 @@ template <> struct Store<float> {
         pf[0] = __fadd2_rn(pf[0], o[0]);
         pf[1] = __fadd2_rn(pf[1], o[1]);
         return pack2v(pf);
+    }
+    __device__ __forceinline__ static uint4 negate(const uint4 &u) {
+        return make_uint4(u.x ^ 0x80000000u, u.y ^ 0x80000000u, u.z ^ 0x80000000u, u.w ^ 0x80000000u);
     }
 };
 

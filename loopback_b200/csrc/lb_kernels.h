@@ -84,6 +84,8 @@ struct ReadBwdParams {
     int rank4;             // as in ReadFwdParams
     int stages;
     int accum;             // 0: dV / dR are written; 1: added into
+    int finalize;          // 1: also add the key-scale gradient term of source n-1 into dV[n-1] (its last reader)
+    void *neg_out;         // [n_tok][d] or null: receives -dV[n-1] when finalize is set
     float inv_sqrt_d;
     int *err_word;
 };

@@ -34,6 +34,7 @@ struct BwdSmemTail {
     float mass;
     int abort_flag;
     float xch[2][kBwdMaxNcw];                   // partial g.v of the token's warps, double buffered by source
+    float fin[kBwdMaxNcw];                      // per token: coefficient of the key-scale term of the finalised source
     uint64_t full[kBwdMaxStages];
     uint64_t empty[kBwdMaxStages];
     uint64_t sfull[2];
@@ -78,7 +79,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     const uint32_t tail_a = (qsm_a + (uint32_t)(FR * WPT * 32 * V4) * 16u + 15u) & ~15u;
     const uint32_t c0_a = tail_a + offsetof(BwdSmemTail, c0), lc_a = tail_a + offsetof(BwdSmemTail, lc);
     const uint32_t mass_a = tail_a + offsetof(BwdSmemTail, mass), abort_a = tail_a + offsetof(BwdSmemTail, abort_flag);
-    const uint32_t xch_a = tail_a + offsetof(BwdSmemTail, xch);
+    const uint32_t xch_a = tail_a + offsetof(BwdSmemTail, xch), fin_a = tail_a + offsetof(BwdSmemTail, fin);
     const uint32_t full_a = tail_a + offsetof(BwdSmemTail, full), empty_a = tail_a + offsetof(BwdSmemTail, empty);
     const uint32_t sfull_a = tail_a + offsetof(BwdSmemTail, sfull), sempty_a = tail_a + offsetof(BwdSmemTail, sempty);
 
@@ -191,9 +192,6 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     }
                     dot = warp_sum((d2a.x + d2b.x) + (d2a.y + d2b.y));
                     if (WPT > 1 && lane == 0) sts_f32(xch_a + 4u * ((i & 1) * kBwdMaxNcw + warp), dot);
-                } else {
-#pragma unroll
-                    for (int k = 0; k < FR; ++k) raw[k] = zero4;
                 }
                 if (i > 0) {
                     const uint32_t j4 = (uint32_t)(i - 1) * BT4;
@@ -222,8 +220,10 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 }
                 if (WPT > 1) named_bar_sync(bar_id, bar_threads);
                 dot_prev = dot;
+                if (i < n) {                      // after the loop vprev still holds source n - 1 (used by phase 2)
 #pragma unroll
-                for (int k = 0; k < FR; ++k) vprev[k] = raw[k];
+                    for (int k = 0; k < FR; ++k) vprev[k] = raw[k];
+                }
             }
             // ---- query-gradient partial of this thread's columns: private shared-memory slots
             if (alive && tok_in) {
@@ -250,8 +250,10 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     const float gp = mass * (gd + lds_f32(tb + 2u * tfl4 + i4));
                     const float dz = pi * (gp - sacc);
                     sts_f32(gk + i4, dz * ri * inv);
+                    const float drtot = lds_f32(tb + 5u * tfl4 + i4) + dz * lds_f32(tb + 4u * tfl4 + i4);
+                    if (p.finalize && i == n - 1) sts_f32(fin_a + t4, drtot * (-(ri * ri * ri)) / (float)p.d);
                     if (alive && tok_in) {
-                        p.dR[(long long)i * p.n_tok + tok] = lds_f32(tb + 5u * tfl4 + i4) + dz * lds_f32(tb + 4u * tfl4 + i4);
+                        p.dR[(long long)i * p.n_tok + tok] = drtot;
                         p.dcbar[tok * n + i] = -gd;
                     }
                 }
@@ -291,8 +293,22 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     float2 o[P];
 #pragma unroll
                     for (int e = 0; e < P; ++e) o[e] = __ffma2_rn(w2, g2[k][e], __fmul2_rn(kq2, q2[k][e]));
-                    const uint4 res = p.accum ? S::accum(prev[k], o) : S::pack2v(o);
+                    uint4 res = p.accum ? S::accum(prev[k], o) : S::pack2v(o);
                     const int col = (chunk0 + k) * BW + lane * VEC;
+                    if (p.finalize && i == n - 1) {
+                        // this read is the last to touch source n-1: add the gradient that reaches the update through
+                        // its key scale, dR (-r^3/d) v, rounded like the separate accumulation kernel would, and hand
+                        // out the negated total (the gradient of the block input)
+                        const float kf = lds_f32(fin_a + t4);
+                        const float2 kf2 = make_float2(kf, kf);
+                        float2 vf[P], kv[P];
+                        S::unpack2(vprev[k], vf);
+#pragma unroll
+                        for (int e = 0; e < P; ++e) kv[e] = __fmul2_rn(kf2, vf[e]);
+                        res = S::accum(res, kv);
+                        if (p.neg_out != nullptr && alive && tok_in && col < p.d)
+                            st_global_v4(reinterpret_cast<T *>(p.neg_out) + tok * (long long)p.d + col, S::negate(res));
+                    }
                     if (alive && tok_in && col < p.d) st_global_v4(dvrow + k * BW, res);
                 }
                 dvrow += src_stride;
@@ -416,17 +432,14 @@ static cudaError_t launch_bwd(const CUtensorMap &tmV, const CUtensorMap &tmG, co
 
 cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmG,
                             const CUtensorMap &tmDV, const ReadBwdParams &p, int grid, cudaStream_t stream) {
-#define LB_BWD_CASE(TT, F, W) return launch_bwd<TT, F, W>(tmV, tmG, tmDV, p, grid, stream)
-#define LB_BWD_FR(TT, W) \
-    switch (fr) { case 1: LB_BWD_CASE(TT, 1, W); case 2: LB_BWD_CASE(TT, 2, W); case 3: LB_BWD_CASE(TT, 3, W); default: break; }
-    if (dtype == LB_DTYPE_BF16) {
-        if (ncw == 16) { LB_BWD_FR(__nv_bfloat16, 16) }
-        else if (ncw == 8) { LB_BWD_FR(__nv_bfloat16, 8) if (fr == 4) LB_BWD_CASE(__nv_bfloat16, 4, 8); }
-    } else {
-        if (ncw == 16) { LB_BWD_FR(float, 16) }
-        else if (ncw == 8) { LB_BWD_FR(float, 8) if (fr == 4) LB_BWD_CASE(float, 4, 8); }
-    }
-#undef LB_BWD_FR
+    // instantiated shapes: 16 consumer warps x {1,2} fragments, 12 x {1,2}, 8 x {1,2,3,4}
+#define LB_BWD_CASE(TT, F, W) \
+    if (fr == F && ncw == W) return launch_bwd<TT, F, W>(tmV, tmG, tmDV, p, grid, stream);
+#define LB_BWD_ALL(TT)                                                                                   \
+    LB_BWD_CASE(TT, 1, 16) LB_BWD_CASE(TT, 2, 16) LB_BWD_CASE(TT, 1, 12) LB_BWD_CASE(TT, 2, 12)          \
+    LB_BWD_CASE(TT, 1, 8) LB_BWD_CASE(TT, 2, 8) LB_BWD_CASE(TT, 3, 8) LB_BWD_CASE(TT, 4, 8)
+    if (dtype == LB_DTYPE_BF16) { LB_BWD_ALL(__nv_bfloat16) } else { LB_BWD_ALL(float) }
+#undef LB_BWD_ALL
 #undef LB_BWD_CASE
     return cudaErrorInvalidValue;
 }

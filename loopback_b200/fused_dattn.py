@@ -130,14 +130,24 @@ def _timed(kind, n, accum=False):
     return _NoTimer() if LAUNCH_TIMER is None else LAUNCH_TIMER(kind, n, accum)
 
 
-def _launch_read_bwd(V, R, dV, dR, qc, g, gt, cbar, c0, lg, lse, lse0, scratch, n_tok, d, N, n, accum):
+def _launch_read_bwd(V, R, dV, dR, qc, g, gt, cbar, c0, lg, lse, lse0, scratch, n_tok, d, N, n, accum,
+                     finalize=False, neg_out=None):
+    """One backward read. With `finalize` the kernel also completes dV[n - 1] (adds the gradient that reaches the
+    update through its key scale) and writes its negation to `neg_out`."""
     dev = V.device
     dcbar = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
     dq = torch.empty(d, device=dev, dtype=torch.float32)
     with torch.cuda.device(dev), _timed("read_bwd", n, accum):
-        check(_lib.lib().lb_read_bwd(ptr(V), ptr(R), ptr(dV), ptr(dR), ptr(qc), ptr(g), ptr(gt), ptr(cbar), ptr(c0),
-                                     ptr(lg), ptr(lse), ptr(lse0), ptr(dcbar), ptr(dq), ptr(scratch), n_tok, d, N, n,
-                                     int(bool(accum)), dtype_code(V.dtype), stream_ptr()), "read backward")
+        if finalize:
+            check(_lib.lib().lb_read_bwd_final(ptr(V), ptr(R), ptr(dV), ptr(dR), ptr(qc), ptr(g), ptr(gt), ptr(cbar),
+                                               ptr(c0), ptr(lg), ptr(lse), ptr(lse0), ptr(dcbar), ptr(dq),
+                                               ptr(scratch), ptr(neg_out), n_tok, d, N, n, int(bool(accum)),
+                                               dtype_code(V.dtype), stream_ptr()), "read backward (final)")
+        else:
+            check(_lib.lib().lb_read_bwd(ptr(V), ptr(R), ptr(dV), ptr(dR), ptr(qc), ptr(g), ptr(gt), ptr(cbar),
+                                         ptr(c0), ptr(lg), ptr(lse), ptr(lse0), ptr(dcbar), ptr(dq), ptr(scratch),
+                                         n_tok, d, N, n, int(bool(accum)), dtype_code(V.dtype), stream_ptr()),
+                  "read backward")
     return dq, dcbar
 
 
@@ -213,7 +223,8 @@ class DattnStack:
     (n_steps - 1, d); read s uses row s - 1) each write also stores the update's scores against the queries of the
     reads that will see it, DOTS[query, update, token] fp32, and the reads use those; the queries are taken as they
     are when the stack is built, i.e. for one forward pass."""
-    __slots__ = ("V", "R", "dV", "dR", "n_steps", "n_tok", "d", "eps", "Q", "QT", "DOTS", "r_done", "_scratch")
+    __slots__ = ("V", "R", "dV", "dR", "n_steps", "n_tok", "d", "eps", "Q", "QT", "DOTS", "r_done", "_scratch",
+                 "fuse_final", "_scale_done", "_neg")
 
     def __init__(self, n_steps: int, shape, dtype, device, query=None, eps: float = 1e-6):
         b, t, d = shape
@@ -233,6 +244,12 @@ class DattnStack:
         self.r_done = [False] * self.n_steps      # R[s] (and the scores of update s) written by the write of s
         self.Q = self.QT = self.DOTS = None
         self._scratch = None
+        # The backward of read s is the last kernel to touch update s, so it also finishes that update's gradient
+        # (the key-scale term, and the negated copy the write hands to the block input) instead of leaving them to
+        # two more passes over it: _scale_done[s] / _neg[s] record what it did for the nodes that follow.
+        self.fuse_final = True
+        self._scale_done = [False] * self.n_steps
+        self._neg = [None] * self.n_steps
         if query is not None:
             self.Q = query.detach().float().contiguous()
             self.DOTS = torch.empty((max(1, self.Q.shape[0]), self.n_steps, b * t), dtype=torch.float32, device=device)
@@ -276,10 +293,18 @@ class _WriteDelta(torch.autograd.Function):
                                       stack.n_tok, stack.d, stack.n_steps, nq, int(s), stack.eps,
                                       dtype_code(stack.V.dtype), stream_ptr()), "write")
         stack.r_done[s] = True
+        ctx.stack, ctx.s = stack, int(s)
         return out
 
     @staticmethod
     def backward(ctx, g: torch.Tensor):
+        stack, s = ctx.stack, ctx.s
+        ctx.stack = None
+        neg = stack._neg[s] if stack is not None else None
+        if neg is not None:
+            stack._neg[s] = None
+            if stack.dV is not None and g.data_ptr() == stack.dV[s].data_ptr() and g.shape == neg.shape:
+                return None, None, g, neg            # the final read of update s already wrote -dV[s]
         gc = g.contiguous()
         dx = torch.empty_like(gc)
         with torch.cuda.device(gc.device):
@@ -306,11 +331,19 @@ class _RstdStk(torch.autograd.Function):
         if stack.dV is None:
             raise RuntimeError("delta_attnres stacked read: the scale's backward ran before any read's backward")
         grc = gr.contiguous().float()
-        xc = x.detach().contiguous()
-        dv_s = stack.dV[s]
-        with torch.cuda.device(xc.device):
-            check(_lib.lib().lb_rstd_bwd_acc(ptr(xc), ptr(stack.R[s]), ptr(grc), ptr(dv_s), stack.n_tok, stack.d,
-                                             dtype_code(xc.dtype), stream_ptr()), "stacked rstd backward")
+        if stack._scale_done[s]:
+            # the final read of update s already added the term for the gradient it produced itself (dR[s]); only a
+            # gradient that reached the scale from elsewhere is still missing
+            stack._scale_done[s] = False
+            grc = None if grc.data_ptr() == stack.dR[s].data_ptr() else grc - stack.dR[s].reshape(grc.shape)
+            if grc is not None:
+                stack._neg[s] = None                 # the negated copy no longer matches
+        if grc is not None:
+            xc = x.detach().contiguous()
+            dv_s = stack.dV[s]
+            with torch.cuda.device(xc.device):
+                check(_lib.lib().lb_rstd_bwd_acc(ptr(xc), ptr(stack.R[s]), ptr(grc), ptr(dv_s), stack.n_tok, stack.d,
+                                                 dtype_code(xc.dtype), stream_ptr()), "stacked rstd backward")
         out = _alias(stack.dV, s)
         ctx.stack = ctx.x = None          # release the stack from this node
         return None, None, out, None
@@ -342,6 +375,9 @@ class FusedDattnReadStk(torch.autograd.Function):
         if save:
             ctx.save_for_backward(qc, cbar_c, c0c, lg, lse, lse0)
         ctx.stack, ctx.step, ctx.n, ctx.q_dtype, ctx.base_shape = stack, int(step), n, q.dtype, base.shape
+        # finish update `step` in this read's backward only if its key scale is part of the graph (it is when the
+        # caller keeps the scales in `keys`, as both models do); otherwise nobody would consume the term
+        ctx.finalize = bool(stack.fuse_final and save and ctx.needs_input_grad[6 + n + int(step)])
         return out, tc.view(*base.shape[:-1], n)
 
     @staticmethod
@@ -352,8 +388,13 @@ class FusedDattnReadStk(torch.autograd.Function):
         accum = stack.grads()
         g = g.contiguous()
         gt_c = None if gt is None else gt.reshape(n_tok, n).float().contiguous()
+        neg = None
+        if ctx.finalize:
+            neg = torch.empty((n_tok, d), device=g.device, dtype=stack.V.dtype).view(stack.V.shape[1:])
+            stack._scale_done[step], stack._neg[step] = True, neg
         dq, dcbar = _launch_read_bwd(stack.V, stack.R, stack.dV, stack.dR, qc, g, gt_c, cbar_c, c0c, lg, lse, lse0,
-                                     stack.scratch(), n_tok, d, stack.n_steps, n, accum)
+                                     stack.scratch(), n_tok, d, stack.n_steps, n, accum,
+                                     finalize=ctx.finalize, neg_out=neg)
         final = [i == step or (step == 1 and i == 0) for i in range(n)]   # the last read of scale i, in backward order
         grads = (None, None, dq.to(ctx.q_dtype), g, dcbar.view(*ctx.base_shape[:-1], n), None,
                  *[None] * n, *[_alias(stack.dR, i) if final[i] else None for i in range(n)])

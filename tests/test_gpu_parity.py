@@ -92,6 +92,54 @@ def test_write_rejects_bad_arguments(L):
                            None, None, 4, 64, 200, 129, 0, None) == -3
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_tok,d,n,accum", [(70, 1024, 5, True), (33, 1536, 3, False), (9, 3072, 4, True),
+                                             (130, 768, 2, True), (5, 64, 6, False), (64, 2048, 7, True)])
+def test_read_bwd_final_equals_the_three_separate_kernels(L, dtype, n_tok, d, n, accum):
+    """lb_read_bwd_final == lb_read_bwd, then lb_rstd_bwd_acc on the newest update, then lb_write_bwd_dx: bit for bit."""
+    N = 8
+    g = torch.Generator(device="cuda").manual_seed(n_tok + d + n)
+    code = L.dtype_code(dtype)
+    V = (torch.randn(N, n_tok, d, device="cuda", generator=g) * 0.5).to(dtype)
+    R = torch.rsqrt(V.float().pow(2).mean(-1) + 1e-6).contiguous()
+    q = (torch.randn(d, device="cuda", generator=g) * 0.3).contiguous()
+    dots = torch.einsum("ntd,d->nt", V.float(), q).contiguous()
+    base = torch.randn(n_tok, d, device="cuda", generator=g).to(dtype)
+    c0 = (torch.rand(n, device="cuda", generator=g) * 0.9 + 0.1).contiguous()
+    cbar = (c0.view(1, -1) + 0.2 * torch.randn(n_tok, n, device="cuda", generator=g)).contiguous()
+    out = torch.empty_like(base)
+    tc, lg = torch.empty(n_tok, n, device="cuda"), torch.empty(n_tok, n, device="cuda")
+    lse, lse0 = torch.empty(n_tok, device="cuda"), torch.empty(n_tok, device="cuda")
+    L.check(L.lib().lb_read_fwd(L.ptr(V), L.ptr(R), L.ptr(dots), 0, L.ptr(base), L.ptr(cbar), L.ptr(c0), L.ptr(out),
+                                L.ptr(tc), L.ptr(lg), L.ptr(lse), L.ptr(lse0), n_tok, d, N, n, code, L.stream_ptr()), "fwd")
+    up = torch.randn(n_tok, d, device="cuda", generator=g).to(dtype)
+    gt = torch.randn(n_tok, n, device="cuda", generator=g)
+    dV0 = torch.randn(N, n_tok, d, device="cuda", generator=g).to(dtype)
+    dR0 = torch.randn(N, n_tok, device="cuda", generator=g)
+    scratch = torch.empty(L.lib().lb_read_bwd_scratch_bytes(d) // 4, device="cuda")
+
+    def args(dV, dR, dcbar, dq):
+        return [L.ptr(V), L.ptr(R), L.ptr(dV), L.ptr(dR), L.ptr(q), L.ptr(up), L.ptr(gt), L.ptr(cbar), L.ptr(c0),
+                L.ptr(lg), L.ptr(lse), L.ptr(lse0), L.ptr(dcbar), L.ptr(dq), L.ptr(scratch)]
+    tail = [n_tok, d, N, n, int(accum), code, L.stream_ptr()]
+    dV1, dR1 = dV0.clone(), dR0.clone()
+    dcb1, dq1 = torch.empty(n_tok, n, device="cuda"), torch.empty(d, device="cuda")
+    L.check(L.lib().lb_read_bwd(*args(dV1, dR1, dcb1, dq1), *tail), "bwd")
+    L.check(L.lib().lb_rstd_bwd_acc(L.ptr(V[n - 1]), L.ptr(R[n - 1]), L.ptr(dR1[n - 1]), L.ptr(dV1[n - 1]), n_tok, d, code,
+                                    L.stream_ptr()), "rstd acc")
+    neg1 = torch.empty(n_tok, d, device="cuda", dtype=dtype)
+    L.check(L.lib().lb_write_bwd_dx(L.ptr(dV1[n - 1]), L.ptr(neg1), n_tok * d, code, L.stream_ptr()), "neg")
+    dV2, dR2 = dV0.clone(), dR0.clone()
+    dcb2, dq2 = torch.empty(n_tok, n, device="cuda"), torch.empty(d, device="cuda")
+    neg2 = torch.full((n_tok, d), float("nan"), device="cuda", dtype=dtype)
+    L.check(L.lib().lb_read_bwd_final(*args(dV2, dR2, dcb2, dq2), L.ptr(neg2), *tail), "bwd final")
+    torch.cuda.synchronize()
+    assert torch.equal(dV1[:n], dV2[:n]) and torch.equal(dR1[:n], dR2[:n])
+    assert torch.equal(dV1[n:], dV2[n:]), "slices beyond n must not be touched"
+    assert torch.equal(dcb1, dcb2) and torch.equal(dq1, dq2) and torch.equal(neg1, neg2)
+    assert L.device_error() == 0
+
+
 # ------------------------------------------------------------------------------------------------------------
 # 2. one read, list layout, in the style of the reference's kernel test (tests/test_fused_dattn.py:48-108)
 # ------------------------------------------------------------------------------------------------------------
