@@ -37,7 +37,7 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 struct Options {
     int fwd_stages = 0, bwd_stages = 0, fwd_fr = 0, grid_cap = 0, fwd_warps = 0, bwd_warps = 0, bwd_wpt = 0,
-        tma_per_chunk = 0;
+        tma_per_chunk = 0, write_tt = 0;
 } g_opt;
 
 struct DeviceInfo {
@@ -180,6 +180,7 @@ int lb_set_option(const char *name, int value) {
     else if (!strcmp(name, "bwd_warps")) g_opt.bwd_warps = value;
     else if (!strcmp(name, "bwd_wpt")) g_opt.bwd_wpt = value;
     else if (!strcmp(name, "tma_per_chunk")) g_opt.tma_per_chunk = value;
+    else if (!strcmp(name, "write_tt")) g_opt.write_tt = value;
     else return fail(LB_ERR_ARG, "unknown option '%s'", name);
     return LB_OK;
 }
@@ -206,7 +207,7 @@ int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, fl
     if (p.nq <= 0) { p.nq = 0; p.Q = nullptr; }
     p.dots_s = DOTS ? DOTS + (long long)s * n_tok : nullptr;
     p.dots_qstride = (long long)N * n_tok;
-    p.n_tok = n_tok; p.d = d; p.eps = eps;
+    p.n_tok = n_tok; p.d = d; p.eps = eps; p.write_tt = g_opt.write_tt == 1 || g_opt.write_tt == 2 ? g_opt.write_tt : 0;
     cudaError_t e = lb::launch_write(dtype, p, di.sms, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_write launch");
 }

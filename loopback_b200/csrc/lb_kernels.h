@@ -52,6 +52,7 @@ struct WriteParams {
     int j0;                // first query whose read sees this update
     int nq;                // queries j0 .. j0 + nq - 1 are scored
     float eps;
+    int write_tt;          // tokens per lane (1 or 2); 0 = choose by size
 };
 
 cudaError_t launch_write(int dtype, const WriteParams &p, int sms, cudaStream_t stream);

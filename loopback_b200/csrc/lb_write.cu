@@ -5,138 +5,187 @@
 //   DOTS[j, s, t]  = q_j . V[s, t, :]   for the queries j >= max(s - 1, 0), i.e. exactly the reads that see update s
 //
 // Replaces the reference's stacked write kernel (fused_dattn.py:561-585; it scores all queries on tensor cores
-// in three-pass TF32). Here the skinny product runs on the CUDA cores in fp32: 128-bit loads, a register tile of
-// 4 tokens x 8 queries per warp, and a transposing warp-shuffle reduction. DOTS is token-contiguous
-// ([query][update][token]) so that both these stores and the reads' loads are whole sectors.
+// in three-pass TF32). Here the skinny product runs on the CUDA cores in fp32. A CTA takes a tile of 32 or 64 tokens
+// and walks the row in 128-byte chunks: phase A is coalesced (8 lanes per token: 128-bit loads of h and x, the rounded
+// update stored to V and kept as fp32 in shared memory, the next chunk's loads already in flight), phase B turns the
+// tile around -- lanes over tokens, warps over query groups -- so that every lane accumulates complete dot products
+// (packed fma.rn.f32x2, query values broadcast from shared memory) and no cross-lane reduction is needed. DOTS is
+// token-contiguous ([query][update][token]): a warp stores 32 consecutive floats per query.
 #include "lb_common.cuh"
 #include "lb_kernels.h"
 
 namespace lb {
 
-constexpr int kWrTT = 4;     // tokens per warp pass
-constexpr int kWrTQ = 8;     // queries per register tile
+// Tile of the write kernel: 32 * TT tokens x all columns, walked in chunks of 128 bytes per token
+// (64 bf16 / 32 fp32 columns). 4 warps per CTA; warp w scores queries [w * QPT, (w + 1) * QPT) of the queries that
+// will read this update, lane l owns tokens l (and l + 32 when TT == 2) of the tile.
+constexpr int kWrThreads = 128;
+constexpr int kWrChunkBytes = 128;
 
-// sum of vals[l] over all lanes, delivered to lane l (31 shuffles for 32 values)
-__device__ __forceinline__ float transpose_reduce32(float (&vals)[32], int lane) {
-#pragma unroll
-    for (int s = 16; s >= 1; s >>= 1) {
-        const bool up = (lane & s) != 0;
-#pragma unroll
-        for (int k = 0; k < s; ++k) {
-            const float send = up ? vals[k] : vals[k + s];
-            const float keep = up ? vals[k + s] : vals[k];
-            vals[k] = keep + __shfl_xor_sync(0xffffffffu, send, s);
-        }
-    }
-    return vals[0];
-}
-
-template <typename T>
-__global__ void __launch_bounds__(256) write_kernel(WriteParams p) {
+template <typename T, int TT, int QPT>
+__global__ void __launch_bounds__(kWrThreads) write_kernel(WriteParams p) {
     using S = Store<T>;
     constexpr int VEC = S::kVec;
-    extern __shared__ uint4 wr_smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int warps = blockDim.x >> 5;
-    const int d = p.d;
-    const int frags_per_row = d / VEC;                        // 16-byte fragments per token row
-    uint4 *vt = wr_smem + (size_t)warp * kWrTT * frags_per_row;   // this warp's [4][d] update tile
+    constexpr int KC = kWrChunkBytes / S::kBytes;         // columns per chunk
+    constexpr int FPT = KC / VEC;                         // 16-byte fragments per token and chunk (8)
+    constexpr int TB = 32 * TT;                           // tokens per tile
+    constexpr int FRG = TB * FPT / kWrThreads;            // fragments per thread and chunk (2 * TT)
+    constexpr int VS = KC + 4;                            // padded row of the fp32 update tile (conflict-free LDS.128)
+    constexpr int NQP = 4 * QPT;                          // query rows held per chunk (zero rows past nq)
+    constexpr int QF4 = (NQP * KC / 4 + kWrThreads - 1) / kWrThreads;   // float4 of the query chunk per thread
+    static_assert(FRG * kWrThreads == TB * FPT, "tile shape");
+
+    extern __shared__ float4 wr_smem4[];
+    float *vs = reinterpret_cast<float *>(wr_smem4);                  // [2][TB][VS]
+    float *qs = vs + 2 * TB * VS;                                     // [2][NQP][KC]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int d = p.d, nq = p.nq;
+    const long long tok0 = (long long)blockIdx.x * TB;
     const T *h = static_cast<const T *>(p.h);
     const T *x = static_cast<const T *>(p.x);
     T *vout = static_cast<T *>(p.v);
-    const long long groups = (p.n_tok + kWrTT - 1) / kWrTT;
+    const int nchunks = (d + KC - 1) / KC;
+    const bool scores = p.Q != nullptr && nq > 0;
 
-    for (long long grp = (long long)blockIdx.x * warps + warp; grp < groups; grp += (long long)gridDim.x * warps) {
-        const long long tok0 = grp * kWrTT;
-        float ss[kWrTT] = {0.f, 0.f, 0.f, 0.f};
-        // ---- phase A: the update, its store, its sum of squares; the rounded update stays in shared memory
-        for (int f = lane; f < frags_per_row; f += 32) {
-            uint4 hu[kWrTT], xu[kWrTT];
+    // phase A fragments of this thread: token (tid >> 3) + 16 m, fragment tid & 7 of the chunk
+    const int fr = tid & (FPT - 1);
+    uint4 hraw[FRG], xraw[FRG];
+    auto fetch = [&](int c) {
+        const int col = c * KC + fr * VEC;
 #pragma unroll
-            for (int t = 0; t < kWrTT; ++t) {
-                const long long tok = min(tok0 + t, p.n_tok - 1);
-                hu[t] = ld_global_stream_v4(h + tok * d + f * VEC);
-                xu[t] = ld_global_stream_v4(x + tok * d + f * VEC);
+        for (int m = 0; m < FRG; ++m) {
+            const long long tok = min(tok0 + (tid >> 3) + 16 * m, p.n_tok - 1);
+            if (col < d) {
+                hraw[m] = ld_global_stream_v4(h + tok * d + col);
+                xraw[m] = ld_global_stream_v4(x + tok * d + col);
+            } else {
+                hraw[m] = make_uint4(0, 0, 0, 0);
+                xraw[m] = make_uint4(0, 0, 0, 0);
             }
+        }
+    };
+
+    float2 acc[TT][QPT];
+    float2 ss[TT];
 #pragma unroll
-            for (int t = 0; t < kWrTT; ++t) {
+    for (int t = 0; t < TT; ++t) {
+        ss[t] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int jj = 0; jj < QPT; ++jj) acc[t][jj] = make_float2(0.f, 0.f);
+    }
+
+    fetch(0);
+    for (int c = 0; c < nchunks; ++c) {
+        const int buf = c & 1;
+        float *vb = vs + buf * TB * VS;
+        float *qb = qs + buf * NQP * KC;
+        // ---- phase A: the update of this chunk -> HBM (rounded once) and, as fp32, -> shared memory
+        {
+            const int col = c * KC + fr * VEC;
+#pragma unroll
+            for (int m = 0; m < FRG; ++m) {
+                const int tl = (tid >> 3) + 16 * m;
                 float hf[VEC], xf[VEC], vf[VEC];
-                S::unpack(hu[t], hf);
-                S::unpack(xu[t], xf);
+                S::unpack(hraw[m], hf);
+                S::unpack(xraw[m], xf);
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) vf[e] = hf[e] - xf[e];
                 const uint4 packed = S::pack(vf);
                 S::unpack(packed, vf);                                   // the stored (rounded) values
+                if (col < d && tok0 + tl < p.n_tok) st_global_v4(vout + (tok0 + tl) * d + col, packed);
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) ss[t] = fmaf(vf[e], vf[e], ss[t]);
-                vt[t * frags_per_row + f] = packed;
-                if (tok0 + t < p.n_tok) st_global_v4(vout + (tok0 + t) * d + f * VEC, packed);
+                for (int e4 = 0; e4 < VEC / 4; ++e4)
+                    *reinterpret_cast<float4 *>(vb + tl * VS + fr * VEC + 4 * e4) =
+                        make_float4(vf[4 * e4], vf[4 * e4 + 1], vf[4 * e4 + 2], vf[4 * e4 + 3]);
             }
-        }
+            if (scores) {
 #pragma unroll
-        for (int t = 0; t < kWrTT; ++t) ss[t] = warp_sum(ss[t]);
-        if (p.r != nullptr && lane < kWrTT && tok0 + lane < p.n_tok) {
-            const float mine = lane == 0 ? ss[0] : (lane == 1 ? ss[1] : (lane == 2 ? ss[2] : ss[3]));
-            p.r[tok0 + lane] = rsqrtf(mine / (float)d + p.eps);
-        }
-        if (p.Q == nullptr || p.nq <= 0) continue;
-        __syncwarp();
-        // ---- phase B: scores of the 4 tokens against the queries that will read this update
-        for (int jg = 0; jg < p.nq; jg += kWrTQ) {
-            float acc[32];
-#pragma unroll
-            for (int k = 0; k < 32; ++k) acc[k] = 0.f;
-            for (int f = lane; f < frags_per_row; f += 32) {
-                float vf[kWrTT][VEC];
-#pragma unroll
-                for (int t = 0; t < kWrTT; ++t) S::unpack(vt[t * frags_per_row + f], vf[t]);
-#pragma unroll
-                for (int jj = 0; jj < kWrTQ; ++jj) {
-                    const int j = min(jg + jj, p.nq - 1) + p.j0;      // clamped: surplus lanes recompute the last query
-                    const float4 *qp = reinterpret_cast<const float4 *>(p.Q + (long long)j * d + f * VEC);
-                    float qf[VEC];
-#pragma unroll
-                    for (int e4 = 0; e4 < VEC / 4; ++e4) {
-                        const float4 q4 = __ldg(qp + e4);
-                        qf[4 * e4] = q4.x; qf[4 * e4 + 1] = q4.y; qf[4 * e4 + 2] = q4.z; qf[4 * e4 + 3] = q4.w;
-                    }
-#pragma unroll
-                    for (int t = 0; t < kWrTT; ++t)
-#pragma unroll
-                        for (int e = 0; e < VEC; ++e) acc[t * kWrTQ + jj] = fmaf(vf[t][e], qf[e], acc[t * kWrTQ + jj]);
+                for (int m = 0; m < QF4; ++m) {
+                    const int idx = tid + kWrThreads * m;
+                    const int jj = idx / (KC / 4), k4 = idx - jj * (KC / 4);
+                    const int qcol = c * KC + 4 * k4;
+                    float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (jj < nq && qcol < d) q4 = __ldg(reinterpret_cast<const float4 *>(p.Q + (long long)(p.j0 + jj) * d + qcol));
+                    if (jj < NQP) *reinterpret_cast<float4 *>(qb + jj * KC + 4 * k4) = q4;
                 }
             }
-            const float tot = transpose_reduce32(acc, lane);       // lane = t * 8 + jj
-            const int t = lane / kWrTQ, jj = lane % kWrTQ;
-            if (jg + jj < p.nq && tok0 + t < p.n_tok)
-                p.dots_s[(long long)(p.j0 + jg + jj) * p.dots_qstride + tok0 + t] = tot;
         }
-        __syncwarp();
+        if (c + 1 < nchunks) fetch(c + 1);           // in flight while this chunk is scored
+        __syncthreads();
+        // ---- phase B: lanes over tokens; every lane holds complete partial dots, no cross-lane reduction
+#pragma unroll 4
+        for (int k4 = 0; k4 < KC / 4; ++k4) {
+            float4 v4[TT];
+#pragma unroll
+            for (int t = 0; t < TT; ++t) v4[t] = *reinterpret_cast<const float4 *>(vb + (lane + 32 * t) * VS + 4 * k4);
+            if (warp == 0) {
+#pragma unroll
+                for (int t = 0; t < TT; ++t) {
+                    ss[t] = __ffma2_rn(make_float2(v4[t].x, v4[t].y), make_float2(v4[t].x, v4[t].y), ss[t]);
+                    ss[t] = __ffma2_rn(make_float2(v4[t].z, v4[t].w), make_float2(v4[t].z, v4[t].w), ss[t]);
+                }
+            }
+            if (scores) {
+#pragma unroll
+                for (int jj = 0; jj < QPT; ++jj) {
+                    const float4 q4 = *reinterpret_cast<const float4 *>(qb + (warp * QPT + jj) * KC + 4 * k4);
+#pragma unroll
+                    for (int t = 0; t < TT; ++t) {
+                        acc[t][jj] = __ffma2_rn(make_float2(v4[t].x, v4[t].y), make_float2(q4.x, q4.y), acc[t][jj]);
+                        acc[t][jj] = __ffma2_rn(make_float2(v4[t].z, v4[t].w), make_float2(q4.z, q4.w), acc[t][jj]);
+                    }
+                }
+            }
+        }
     }
+    // ---- results: one key scale per token, one score per (query, token); lanes are consecutive tokens
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+        const long long tok = tok0 + lane + 32 * t;
+        if (tok >= p.n_tok) continue;
+        if (warp == 0 && p.r != nullptr) p.r[tok] = rsqrtf((ss[t].x + ss[t].y) / (float)d + p.eps);
+        if (scores) {
+#pragma unroll
+            for (int jj = 0; jj < QPT; ++jj) {
+                const int j = warp * QPT + jj;
+                if (j < nq) p.dots_s[(long long)(p.j0 + j) * p.dots_qstride + tok] = acc[t][jj].x + acc[t][jj].y;
+            }
+        }
+    }
+}
+
+template <typename T, int TT, int QPT>
+static cudaError_t launch_write_t(const WriteParams &p, cudaStream_t stream) {
+    constexpr int KC = kWrChunkBytes / Store<T>::kBytes;
+    const size_t smem = sizeof(float) * (2 * 32 * TT * (KC + 4) + 2 * 4 * QPT * KC);
+    cudaError_t e = cudaFuncSetAttribute(write_kernel<T, TT, QPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const long long tiles = (p.n_tok + 32 * TT - 1) / (32 * TT);
+    write_kernel<T, TT, QPT><<<(unsigned)tiles, kWrThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t launch_write_d(const WriteParams &p, int tt, cudaStream_t stream) {
+    const int qpt = p.Q && p.nq > 0 ? (p.nq + 3) / 4 : 0;
+#define LB_WR(Q_) return tt == 2 ? launch_write_t<T, 2, Q_>(p, stream) : launch_write_t<T, 1, Q_>(p, stream)
+    if (qpt <= 2) LB_WR(2);
+    if (qpt <= 4) LB_WR(4);
+    if (qpt <= 6) LB_WR(6);
+    if (qpt <= 12) LB_WR(12);
+    if (qpt <= 20) LB_WR(20);
+    LB_WR(32);
+#undef LB_WR
 }
 
 cudaError_t launch_write(int dtype, const WriteParams &p, int sms, cudaStream_t stream) {
     if (p.n_tok == 0) return cudaSuccess;
-    const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
-    const size_t per_warp = (size_t)kWrTT * p.d * elem;
-    int warps = 8;
-    while (warps > 1 && per_warp * warps > 96 * 1024) warps >>= 1;
-    const size_t smem = per_warp * warps;
-    const long long groups = (p.n_tok + kWrTT - 1) / kWrTT;
-    long long blocks = (groups + warps - 1) / warps;
-    const long long cap = (long long)sms * 16;
-    const int grid = (int)(blocks < cap ? blocks : cap);
-    cudaError_t e;
-    if (dtype == LB_DTYPE_BF16) {
-        e = cudaFuncSetAttribute(write_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        write_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(p);
-    } else {
-        e = cudaFuncSetAttribute(write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        write_kernel<float><<<grid, warps * 32, smem, stream>>>(p);
-    }
-    return cudaGetLastError();
+    if (p.nq > 128) return cudaErrorInvalidValue;
+    // two tokens per lane halve the shared-memory traffic per score; one token per lane gives twice the CTAs
+    // (better balance when the tiles do not fill the SMs several times over)
+    const int tt = p.write_tt ? p.write_tt : (p.n_tok >= (long long)sms * 64 * 6 ? 2 : 1);
+    return dtype == LB_DTYPE_BF16 ? launch_write_d<__nv_bfloat16>(p, tt, stream) : launch_write_d<float>(p, tt, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------
