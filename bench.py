@@ -96,6 +96,7 @@ def cpu_pass_tokens_per_s(w, sample_tokens: int, repeats: int, warmup: int):
 
     from oracle import c_oracle as CO
     CO.build()
+    CO.set_num_threads(os.cpu_count() or 1)      # all host cores, whatever OMP_NUM_THREADS the launcher exported
     N, d = w["K"] * w["R"], w["d"]
     rng = np.random.default_rng(0)
     h0 = rng.standard_normal((sample_tokens, d), dtype=np.float32)

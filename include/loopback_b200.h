@@ -126,6 +126,24 @@ int lb_read_bwd_final(const void *V, const float *R, void *dV, float *dR, const 
                       const float *LSE0, float *dcbar, float *dq, void *scratch, void *neg_out, int64_t n_tok, int d,
                       int N, int n, int accum, int dtype, void *stream);
 
+/* lb_read_fwd with the caller's prologue folded in (LoopDeltaAttnRes.combine, looped_transformer.py:380-391):
+ *   base = proposal                                   when h0 == NULL (a read inside an iteration)
+ *        = proposal + beta * (h0 - proposal)          at the end of an iteration, each operation rounded to the storage
+ *                                                     dtype as the caller's tensor arithmetic would round it
+ *   cbar = lam * (tc_prev, 1)                         tc_prev [n_tok][n-1] = the previous read's TC; lam = 1 or 1 - beta
+ * Needs n >= 2. Everything else as lb_read_fwd. */
+int lb_combine_fwd(const void *V, const float *R, const float *DOTS, int qi, const void *proposal, const void *h0,
+                   float beta, const float *tc_prev, float lam, const float *c0, void *out, float *TC, float *LG,
+                   float *LSE, float *LSE0, int64_t n_tok, int d, int N, int n, int dtype, void *stream);
+
+/* Backward of lb_combine_fwd: as lb_read_bwd / lb_read_bwd_final (finalize != 0, neg_out may be NULL), with the
+ * installed coefficients given as (tc_prev, lam) and dtc_prev [n_tok][n-1] = dL/d tc_prev written instead of dcbar.
+ * dL/d base is g; the caller applies the blend's factors (1 - beta to the proposal, beta to h0). */
+int lb_combine_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
+                   const float *tc_prev, float lam, const float *c0, const float *LG, const float *LSE,
+                   const float *LSE0, float *dtc_prev, float *dq, void *scratch, void *neg_out, int finalize,
+                   int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream);
+
 /* The widest row lb_read_bwd_noalloc accepts. */
 #define LB_NOALLOC_MAX_D 3072
 

@@ -10,6 +10,7 @@ switch: inputs the kernels cannot take raise instead of silently taking an eager
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 from torch import nn
 
@@ -36,6 +37,27 @@ class LoopDeltaAttnRes(nn.Module):
         with torch.no_grad():
             self.query.zero_()
 
+    def prior_rows(self, device) -> torch.Tensor:
+        """[N, N] fp32 on `device`: row s holds, in its first s + 1 entries, the prior of read s -- built on the host
+        exactly as the reads build it step by step (append 1; multiply everything by 1 - beta when an iteration
+        ends, in fp32), so a pass needs no per-read cat / multiply kernels for it."""
+        key = str(torch.device(device))
+        cache = self.__dict__.setdefault("_prior_cache", {})
+        if key not in cache:
+            N = self.num_steps
+            table = np.zeros((N, N), np.float32)
+            c = np.zeros(0, np.float32)
+            for s in range(N):
+                c = np.concatenate((c, np.ones(1, np.float32)))
+                if s % self.num_blocks == self.num_blocks - 1:
+                    c = (np.float32(1.0 - self.beta) * c).astype(np.float32)
+                table[s, :s + 1] = c
+            cache[key] = (torch.from_numpy(table).to(device), float(self.beta))
+        if cache[key][1] != float(self.beta):
+            del cache[key]
+            return self.prior_rows(device)
+        return cache[key][0]
+
     def new_stack(self, shape, dtype, device, scores: bool = True) -> FD.DattnStack:
         """The per-forward storage the model creates before its loop over the shared blocks (the trainer model's
         forward does this inline); `scores` caches each update's scores at its write (LOOP_DATTN_DOTS)."""
@@ -60,6 +82,19 @@ class LoopDeltaAttnRes(nn.Module):
             raise ValueError(f"delta_attnres step {step} received {len(deltas)} deltas, expected {step + 1}")
 
         closes_iteration = block_idx == self.num_blocks - 1
+        if stack is not None and step >= 1 and coeffs is not None and proposal.is_contiguous() \
+                and (not closes_iteration or h0.is_contiguous()):
+            rows = self.prior_rows(proposal.device)
+            if prior_coeffs is not None and prior_coeffs.data_ptr() == rows[step - 1].data_ptr():
+                # the whole prologue (boundary blend, appended 1, decay) runs inside the kernels
+                if keys is not None and len(keys) < len(deltas):
+                    keys.append(stack.rstd(step, deltas[-1], self.eps))
+                scales = keys if keys is not None else [FD._alias(stack.R, i) for i in range(len(deltas))]
+                c0 = rows[step, :step + 1]
+                out, tc = FD.FusedCombineStk.apply(stack, step, self.query[step - 1], proposal,
+                                                   h0 if closes_iteration else None, self.beta, coeffs,
+                                                   1.0 - self.beta if closes_iteration else 1.0, c0, *deltas, *scales)
+                return out, tc, c0
         base = proposal + self.beta * (h0 - proposal) if closes_iteration else proposal
         ones_tok = torch.ones(*proposal.shape[:-1], 1, device=proposal.device, dtype=torch.float32)
         ones_one = torch.ones(1, device=proposal.device, dtype=torch.float32)
@@ -73,6 +108,8 @@ class LoopDeltaAttnRes(nn.Module):
             if keys is not None and len(keys) < len(deltas):
                 keys.append(stack.rstd(step, deltas[-1], self.eps))
             if step == 0:
+                if prior_coeffs is None:
+                    c0 = self.prior_rows(proposal.device)[0, :1]      # same values; lets the next reads fuse
                 return base, cbar, c0
             scales = keys if keys is not None else [FD._alias(stack.R, i) for i in range(len(deltas))]
             out, tc = FD.FusedDattnReadStk.apply(stack, step, self.query[step - 1], base.contiguous(), cbar, c0,

@@ -268,12 +268,35 @@ int lb_scores(const void *V, const float *q, float *dots, int64_t n_tok, int d, 
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_scores launch");
 }
 
+static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int qi, const void *base, const void *h0,
+                         float beta, const float *cbar, const float *tc_prev, float lam, const float *c0, void *out,
+                         float *TC, float *LG, float *LSE, float *LSE0, int64_t n_tok, int d, int N, int n, int dtype,
+                         void *stream);
+
 int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const void *base, const float *cbar,
                 const float *c0, void *out, float *TC, float *LG, float *LSE, float *LSE0, int64_t n_tok, int d, int N,
                 int n, int dtype, void *stream) {
+    if (!cbar) return fail(LB_ERR_ARG, "lb_read_fwd: NULL pointer");
+    return read_fwd_impl(V, R, DOTS, qi, base, nullptr, 0.f, cbar, nullptr, 1.f, c0, out, TC, LG, LSE, LSE0, n_tok, d, N, n,
+                         dtype, stream);
+}
+
+int lb_combine_fwd(const void *V, const float *R, const float *DOTS, int qi, const void *proposal, const void *h0,
+                   float beta, const float *tc_prev, float lam, const float *c0, void *out, float *TC, float *LG,
+                   float *LSE, float *LSE0, int64_t n_tok, int d, int N, int n, int dtype, void *stream) {
+    if (n < 2 || !tc_prev) return fail(LB_ERR_ARG, "lb_combine_fwd: needs n >= 2 and the previous read's coefficients");
+    if (h0 && !aligned16(h0)) return fail(LB_ERR_ALIGN, "lb_combine_fwd: h0 must be 16-byte aligned");
+    return read_fwd_impl(V, R, DOTS, qi, proposal, h0, beta, nullptr, tc_prev, lam, c0, out, TC, LG, LSE, LSE0, n_tok, d,
+                         N, n, dtype, stream);
+}
+
+static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int qi, const void *base, const void *h0,
+                         float beta, const float *cbar, const float *tc_prev, float lam, const float *c0, void *out,
+                         float *TC, float *LG, float *LSE, float *LSE0, int64_t n_tok, int d, int N, int n, int dtype,
+                         void *stream) {
     int rc = check_common(n_tok, d, dtype);
     if (rc) return rc;
-    if (!V || !R || !DOTS || !base || !cbar || !c0 || !out || !TC) return fail(LB_ERR_ARG, "lb_read_fwd: NULL pointer");
+    if (!V || !R || !DOTS || !base || (!cbar && !tc_prev) || !c0 || !out || !TC) return fail(LB_ERR_ARG, "lb_read_fwd: NULL pointer");
     if ((LG != nullptr) != (LSE != nullptr) || (LG != nullptr) != (LSE0 != nullptr))
         return fail(LB_ERR_ARG, "lb_read_fwd: LG, LSE and LSE0 must be given together");
     if (n < 1 || n > N) return fail(LB_ERR_ARG, "lb_read_fwd: n=%d outside [1, N=%d]", n, N);
@@ -288,8 +311,10 @@ int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const 
     const int nch = chunks_of(d, dtype);
     const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
     const bool rank4 = !g_opt.tma_per_chunk && (d * elem) % lb::kChunkBytes == 0;
-    int ncw = g_opt.fwd_warps == 8 || g_opt.fwd_warps == 16 ? g_opt.fwd_warps : 16;
-    if (n_tok <= 8 * (long long)di.sms && g_opt.fwd_warps == 0) ncw = 8;      // few tokens: smaller tiles, more CTAs
+    // a row of at most 4 chunks is one warp's work (8 tokens x the whole row per tile); wider rows are cut into
+    // column groups of 2 chunks over 16-token tiles; few tokens: the smaller tile, for more CTAs
+    int ncw = g_opt.fwd_warps == 8 || g_opt.fwd_warps == 16 ? g_opt.fwd_warps : (nch <= 4 ? 8 : 16);
+    if (n_tok <= 8 * (long long)di.sms && g_opt.fwd_warps == 0) ncw = 8;
     const long long tok_tiles = (n_tok + ncw - 1) / ncw;
     // fragments per warp: the widest tile that wastes no shared memory, narrowed until the grid fills the GPU
     int fr = g_opt.fwd_fr;
@@ -309,14 +334,16 @@ int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const 
     if (stages > 12) stages = 12;
     while (stages > 2 && lb::read_fwd_smem_bytes(fr, ncw, stages) > kMaxSmem) --stages;
 
-    CUtensorMap tmV, tmB;
+    CUtensorMap tmV, tmB, tmH;
     if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, ncw, rank4 ? fr : 0))) return rc;
     if ((rc = make_map(&tmB, base, dtype, n_tok, d, 0, ncw, rank4 ? fr : 0))) return rc;
+    if ((rc = make_map(&tmH, h0 ? h0 : base, dtype, n_tok, d, 0, ncw, rank4 ? fr : 0))) return rc;
 
     lb::ReadFwdParams p;
     p.R = R;
     p.dots = DOTS + (long long)qi * N * n_tok;
-    p.cbar = cbar; p.c0 = c0; p.out = out; p.TC = TC; p.LG = LG; p.LSE = LSE; p.LSE0 = LSE0;
+    p.cbar = cbar; p.tc_prev = tc_prev; p.lam = lam; p.blend = h0 ? 1 : 0; p.beta = beta;
+    p.c0 = c0; p.out = out; p.TC = TC; p.LG = LG; p.LSE = LSE; p.LSE0 = LSE0;
     p.n_tok = n_tok; p.d = d; p.n = n; p.chunks = nch; p.col_groups = cg; p.tok_tiles = tok_tiles;
     p.stages = stages;
     p.rank4 = rank4 ? 1 : 0;
@@ -326,22 +353,34 @@ int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const 
     int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
     if (cap > kMaxGrid) cap = kMaxGrid;
     const int grid = (int)(tiles < cap ? tiles : cap);
-    cudaError_t e = lb::launch_read_fwd(dtype, fr, ncw, tmV, tmB, p, grid, static_cast<cudaStream_t>(stream));
+    cudaError_t e = lb::launch_read_fwd(dtype, fr, ncw, tmV, tmB, tmH, p, grid, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_read_fwd launch");
 }
 
 size_t lb_read_bwd_scratch_bytes(int d) { return d > 0 ? (size_t)kMaxGrid * (size_t)d * sizeof(float) : 0; }
 
 static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
-                         const float *gt, const float *cbar, const float *c0, const float *LG, const float *LSE,
-                         const float *LSE0, float *dcbar, float *dq, void *scratch, int64_t n_tok, int d, int N, int n,
-                         int accum, int finalize, void *neg_out, int dtype, void *stream);
+                         const float *gt, const float *cbar, const float *tc_prev, float lam, const float *c0,
+                         const float *LG, const float *LSE, const float *LSE0, float *dcbar, float *dq, void *scratch,
+                         int64_t n_tok, int d, int N, int n, int accum, int finalize, void *neg_out, int dtype,
+                         void *stream);
 
 int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
                 const float *cbar, const float *c0, const float *LG, const float *LSE, const float *LSE0, float *dcbar,
                 float *dq, void *scratch, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream) {
-    return read_bwd_impl(V, R, dV, dR, q, g, gt, cbar, c0, LG, LSE, LSE0, dcbar, dq, scratch, n_tok, d, N, n, accum, 0,
-                         nullptr, dtype, stream);
+    if (!cbar) return fail(LB_ERR_ARG, "lb_read_bwd: NULL pointer");
+    return read_bwd_impl(V, R, dV, dR, q, g, gt, cbar, nullptr, 1.f, c0, LG, LSE, LSE0, dcbar, dq, scratch, n_tok, d, N, n,
+                         accum, 0, nullptr, dtype, stream);
+}
+
+int lb_combine_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
+                   const float *tc_prev, float lam, const float *c0, const float *LG, const float *LSE,
+                   const float *LSE0, float *dtc_prev, float *dq, void *scratch, void *neg_out, int finalize,
+                   int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream) {
+    if (n < 2 || !tc_prev) return fail(LB_ERR_ARG, "lb_combine_bwd: needs n >= 2 and the previous read's coefficients");
+    if (neg_out && !aligned16(neg_out)) return fail(LB_ERR_ALIGN, "lb_combine_bwd: neg_out must be 16-byte aligned");
+    return read_bwd_impl(V, R, dV, dR, q, g, gt, nullptr, tc_prev, lam, c0, LG, LSE, LSE0, dtc_prev, dq, scratch, n_tok, d,
+                         N, n, accum, finalize, neg_out, dtype, stream);
 }
 
 int lb_read_bwd_final(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
@@ -349,17 +388,19 @@ int lb_read_bwd_final(const void *V, const float *R, void *dV, float *dR, const 
                       const float *LSE0, float *dcbar, float *dq, void *scratch, void *neg_out, int64_t n_tok, int d,
                       int N, int n, int accum, int dtype, void *stream) {
     if (neg_out && !aligned16(neg_out)) return fail(LB_ERR_ALIGN, "lb_read_bwd_final: neg_out must be 16-byte aligned");
-    return read_bwd_impl(V, R, dV, dR, q, g, gt, cbar, c0, LG, LSE, LSE0, dcbar, dq, scratch, n_tok, d, N, n, accum, 1,
-                         neg_out, dtype, stream);
+    if (!cbar) return fail(LB_ERR_ARG, "lb_read_bwd_final: NULL pointer");
+    return read_bwd_impl(V, R, dV, dR, q, g, gt, cbar, nullptr, 1.f, c0, LG, LSE, LSE0, dcbar, dq, scratch, n_tok, d, N, n,
+                         accum, 1, neg_out, dtype, stream);
 }
 
 static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
-                         const float *gt, const float *cbar, const float *c0, const float *LG, const float *LSE,
-                         const float *LSE0, float *dcbar, float *dq, void *scratch, int64_t n_tok, int d, int N, int n,
-                         int accum, int finalize, void *neg_out, int dtype, void *stream) {
+                         const float *gt, const float *cbar, const float *tc_prev, float lam, const float *c0,
+                         const float *LG, const float *LSE, const float *LSE0, float *dcbar, float *dq, void *scratch,
+                         int64_t n_tok, int d, int N, int n, int accum, int finalize, void *neg_out, int dtype,
+                         void *stream) {
     int rc = check_common(n_tok, d, dtype);
     if (rc) return rc;
-    if (!V || !R || !dV || !dR || !q || !g || !cbar || !c0 || !LG || !LSE || !LSE0 || !dcbar || !dq || !scratch)
+    if (!V || !R || !dV || !dR || !q || !g || (!cbar && !tc_prev) || !c0 || !LG || !LSE || !LSE0 || !dcbar || !dq || !scratch)
         return fail(LB_ERR_ARG, "lb_read_bwd: NULL pointer");
     if (n < 1 || n > N) return fail(LB_ERR_ARG, "lb_read_bwd: n=%d outside [1, N=%d]", n, N);
     if (n > LB_MAX_SOURCES) return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: n=%d exceeds LB_MAX_SOURCES=%d", n, LB_MAX_SOURCES);
@@ -408,7 +449,7 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     if ((rc = make_map(&tmDV, dV, dtype, n_tok, d, N, bt, rank4 ? nch : 0))) return rc;
 
     lb::ReadBwdParams p;
-    p.R = R; p.dR = dR; p.dV = dV; p.q = q; p.gt = gt; p.cbar = cbar; p.c0 = c0; p.LSE = LSE; p.LSE0 = LSE0; p.LG = LG;
+    p.R = R; p.dR = dR; p.dV = dV; p.q = q; p.gt = gt; p.cbar = cbar; p.tc_prev = tc_prev; p.lam = lam; p.c0 = c0; p.LSE = LSE; p.LSE0 = LSE0; p.LG = LG;
     p.dcbar = dcbar; p.dq_part = static_cast<float *>(scratch);
     p.n_tok = n_tok; p.tok_tiles = (n_tok + bt - 1) / bt; p.d = d; p.n = n; p.chunks = nch; p.wpt = wpt;
     p.stages = stages; p.rank4 = rank4 ? 1 : 0; p.accum = accum ? 1 : 0; p.finalize = finalize ? 1 : 0;

@@ -14,7 +14,11 @@ namespace lb {
 struct ReadFwdParams {
     const float *R;        // [N][n_tok] key scales
     const float *dots;     // [N][n_tok] the scores of this read's query (row block of DOTS, or a scratch row block)
-    const float *cbar;     // [n_tok][n] installed coefficients
+    const float *cbar;     // [n_tok][n] installed coefficients (used when tc_prev is null)
+    const float *tc_prev;  // [n_tok][n-1] the previous read's coefficients, or null: cbar = lam * (tc_prev, 1)
+    float lam;             // decay applied with tc_prev (1 inside an iteration, 1 - beta at its end)
+    int blend;             // 1: base = proposal + beta (h0 - proposal) formed in the kernel (tmBase = proposal)
+    float beta;
     const float *c0;       // [n] the read's prior
     void *out;             // [n_tok][d]
     float *TC;             // [n_tok][n]
@@ -35,7 +39,7 @@ struct ReadFwdParams {
 
 size_t read_fwd_smem_bytes(int fr, int ncw, int stages);
 cudaError_t launch_read_fwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmBase,
-                            const ReadFwdParams &p, int grid, cudaStream_t stream);
+                            const CUtensorMap &tmH0, const ReadFwdParams &p, int grid, cudaStream_t stream);
 cudaError_t launch_scores(int dtype, const void *V, const float *q, float *dots, long long n_tok, int d, int n,
                           int sms, cudaStream_t stream);
 
@@ -69,7 +73,9 @@ struct ReadBwdParams {
     void *dV;              // [N][n_tok][d] (stores go here; loads of the old value come through TMA)
     const float *q;        // [d] fp32
     const float *gt;       // [n_tok][n] or null
-    const float *cbar;     // [n_tok][n]
+    const float *cbar;     // [n_tok][n] (used when tc_prev is null)
+    const float *tc_prev;  // [n_tok][n-1] or null: cbar = lam * (tc_prev, 1) and dcbar receives d/d tc_prev [n_tok][n-1]
+    float lam;
     const float *c0;       // [n]
     const float *LSE;      // [n_tok]
     const float *LSE0;     // [n_tok]

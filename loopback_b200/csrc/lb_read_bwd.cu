@@ -254,7 +254,8 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     if (p.finalize && i == n - 1) sts_f32(fin_a + t4, drtot * (-(ri * ri * ri)) / (float)p.d);
                     if (alive && tok_in) {
                         p.dR[(long long)i * p.n_tok + tok] = drtot;
-                        p.dcbar[tok * n + i] = -gd;
+                        if (p.tc_prev == nullptr) p.dcbar[tok * n + i] = -gd;
+                        else if (i < n - 1) p.dcbar[tok * (n - 1) + i] = -(p.lam * gd);      // d/d tc_prev
                     }
                 }
             }
@@ -400,7 +401,8 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 if (tok >= p.n_tok) tok = p.n_tok - 1;
                 const float lg = __ldg(p.LG + tok * n + i);
                 const float lse = __ldg(p.LSE + tok), lse0 = __ldg(p.LSE0 + tok);
-                const float cb = __ldg(p.cbar + tok * n + i);
+                const float cb = p.tc_prev == nullptr ? __ldg(p.cbar + tok * n + i)
+                                                      : (i < n - 1 ? p.lam * __ldg(p.tc_prev + tok * (n - 1) + i) : p.lam);
                 const float gtv = p.gt ? __ldg(p.gt + tok * n + i) : 0.f;
                 const float r = __ldg(p.R + (long long)i * p.n_tok + tok);
                 const float drp = p.accum ? p.dR[(long long)i * p.n_tok + tok] : 0.f;

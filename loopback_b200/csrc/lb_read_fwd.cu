@@ -43,7 +43,8 @@ size_t read_fwd_smem_bytes(int fr, int ncw, int stages) {
 
 template <typename T, int FR, int NCW>
 __global__ void __launch_bounds__((NCW + 1 + kFwdScalarWarps) * 32, 1)
-read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBase, ReadFwdParams p) {
+read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBase,
+                const __grid_constant__ CUtensorMap tmH0, ReadFwdParams p) {
     using S = Store<T>;
     constexpr int VEC = S::kVec;
     constexpr int P = S::kPairs;
@@ -115,6 +116,29 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 if (lane == 0) mbar_arrive(empty_a + 8u * st);
                 if (++st == NS) { st = 0; ph ^= 1u; }
             }
+            if (p.blend) {
+                // end of an iteration: base = proposal + beta (h0 - proposal), evaluated step by step with the
+                // storage type's rounding after each operation, i.e. what the caller's own tensor arithmetic gives
+                // (looped_transformer.py:381)
+                if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+                const float beta = p.beta;
+#pragma unroll
+                for (int k = 0; k < FR; ++k) {
+                    float2 h2[P];
+                    S::unpack2(lds_v4(sb + foff[k]), h2);
+#pragma unroll
+                    for (int e = 0; e < P; ++e) {
+                        const float tx = S::round(__fmul_rn(beta, S::round(__fsub_rn(h2[e].x, acc[k][e].x))));
+                        const float ty = S::round(__fmul_rn(beta, S::round(__fsub_rn(h2[e].y, acc[k][e].y))));
+                        acc[k][e].x = S::round(__fadd_rn(acc[k][e].x, tx));
+                        acc[k][e].y = S::round(__fadd_rn(acc[k][e].y, ty));
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                if (++st == NS) { st = 0; ph ^= 1u; }
+            }
             if (alive && !mbar_wait(sfull_a + 8u * buf, (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
             uint32_t wa = wtab_a + buf * kWtabBytes + 4u * warp;
             for (int i = 0; i < n; ++i, wa += 4u * BT) {
@@ -154,6 +178,8 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         if (lane == 0) {
             tma_prefetch_desc(&tmV);
             tma_prefetch_desc(&tmBase);
+            if (p.blend) tma_prefetch_desc(&tmH0);
+            const int first_item = p.blend ? -2 : -1;      // items: [-2: proposal,] -1: base or h0, 0..n-1: sources
             int st = 0; uint32_t ph = 0;
             int issued = 0;
             bool ok = true;
@@ -163,7 +189,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 const int tok0 = (int)(tt * BT);
                 const int chunk0 = cg * FR;
                 const int nch = min(FR, p.chunks - chunk0);
-                for (int item = -1; item < n; ++item) {
+                for (int item = first_item; item < n; ++item) {
                     if (!mbar_wait(empty_a + 8u * st, ph ^ 1u, wc, kDevWaitEmpty)) {
                         ok = false;
                         break;
@@ -171,13 +197,13 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     const uint32_t sb = stages_a + (uint32_t)st * kStageBytes, fb = full_a + 8u * st;
                     if (p.rank4) {          // one box: FR chunks x BT tokens (chunks past the row are zero-filled)
                         mbar_arrive_expect_tx(fb, kStageBytes);
-                        if (item < 0) tma_load_3d(sb, &tmBase, fb, 0, chunk0, tok0);
+                        if (item < 0) tma_load_3d(sb, (item == first_item) ? &tmBase : &tmH0, fb, 0, chunk0, tok0);
                         else tma_load_4d(sb, &tmV, fb, 0, chunk0, tok0, item);
                     } else {
                         mbar_arrive_expect_tx(fb, (uint32_t)(nch * BT * kChunkBytes));
                         for (int c = 0; c < nch; ++c) {
                             const uint32_t dst = sb + (uint32_t)(c * BT * kChunkBytes);
-                            if (item < 0) tma_load_2d(dst, &tmBase, fb, (chunk0 + c) * BW, tok0);
+                            if (item < 0) tma_load_2d(dst, (item == first_item) ? &tmBase : &tmH0, fb, (chunk0 + c) * BW, tok0);
                             else tma_load_3d(dst, &tmV, fb, (chunk0 + c) * BW, tok0, item);
                         }
                     }
@@ -213,34 +239,56 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             if (!mbar_wait(sempty_a + 8u * buf, (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
                 return;
             const uint32_t wt = wtab_a + buf * kWtabBytes;
-            for (int pass = sw; pass * TPP < BT; pass += kFwdScalarWarps) {
-                const int t = pass * TPP + sub;
-                const long long tok_raw = tt * BT + t;
-                const bool tok_ok = tok_raw < p.n_tok;
-                const long long tok = tok_ok ? tok_raw : p.n_tok - 1;
-                float l[kMaxSources / 32], lcv[kMaxSources / 32], cb[kMaxSources / 32];
+            // This warp's passes over the tile (pass = sw, sw + 4, ...; TPP tokens per pass). All their global loads
+            // are issued before any of them is used, so a tile costs one memory round trip, not one per pass.
+            constexpr int U = (BT + kFwdScalarWarps - 1) / kFwdScalarWarps;     // passes per warp when TPP == 1
+            constexpr int NPL = kMaxSources / 32;
+            float rr[U][NPL], dd[U][NPL], cb[U][NPL];
 #pragma unroll
-                for (int k = 0; k < kMaxSources / 32; ++k) {
+            for (int u = 0; u < U; ++u) {
+                const int t = (sw + kFwdScalarWarps * u) * TPP + sub;
+                const long long tok_raw = tt * BT + t;
+                const long long tok = tok_raw < p.n_tok ? tok_raw : p.n_tok - 1;
+#pragma unroll
+                for (int k = 0; k < NPL; ++k) {
+                    const int i = ii + 32 * k;
+                    rr[u][k] = 0.f; dd[u][k] = 0.f; cb[u][k] = 0.f;
+                    if (t < BT && i < n && (k == 0 || G == 32)) {
+                        rr[u][k] = __ldg(p.R + (long long)i * p.n_tok + tok);
+                        dd[u][k] = __ldg(p.dots + (long long)i * p.n_tok + tok);
+                        // installed coefficients: given, or formed from the previous read's (append 1, decay by lam)
+                        cb[u][k] = p.tc_prev == nullptr ? __ldg(p.cbar + tok * n + i)
+                                                        : (i < n - 1 ? p.lam * __ldg(p.tc_prev + tok * (n - 1) + i) : p.lam);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = (sw + kFwdScalarWarps * u) * TPP + sub;
+                if ((sw + kFwdScalarWarps * u) * TPP >= BT) continue;          // warp-uniform
+                const long long tok_raw = tt * BT + t;
+                const bool tok_ok = tok_raw < p.n_tok && t < BT;
+                const long long tok = tok_raw < p.n_tok ? tok_raw : p.n_tok - 1;
+                float l[NPL], lcv[NPL];
+#pragma unroll
+                for (int k = 0; k < NPL; ++k) {
                     const int i = ii + 32 * k;
                     const bool act = i < n && (k == 0 || G == 32);
-                    l[k] = -INFINITY; lcv[k] = -INFINITY; cb[k] = 0.f;
+                    l[k] = -INFINITY; lcv[k] = -INFINITY;
                     if (act) {
-                        const float r = __ldg(p.R + (long long)i * p.n_tok + tok);
-                        const float dt = __ldg(p.dots + (long long)i * p.n_tok + tok);
-                        cb[k] = __ldg(p.cbar + tok * n + i);
                         lcv[k] = lds_f32(lc_a + 4u * i);
-                        l[k] = dt * r * inv + lcv[k];
+                        l[k] = dd[u][k] * rr[u][k] * inv + lcv[k];
                     }
                 }
                 // the scored softmax and the prior-only softmax go through the same instructions on the same
                 // lanes: with a zero query (l == lc) they agree bit for bit, so tc == c0 and out == base exactly
                 float mx = l[0], mx0 = lcv[0];
 #pragma unroll
-                for (int k = 1; k < kMaxSources / 32; ++k) { mx = fmaxf(mx, l[k]); mx0 = fmaxf(mx0, lcv[k]); }
+                for (int k = 1; k < NPL; ++k) { mx = fmaxf(mx, l[k]); mx0 = fmaxf(mx0, lcv[k]); }
                 mx = group_max(mx, G); mx0 = group_max(mx0, G);
                 float s = 0.f, s0 = 0.f;
 #pragma unroll
-                for (int k = 0; k < kMaxSources / 32; ++k) {
+                for (int k = 0; k < NPL; ++k) {
                     const int i = ii + 32 * k;
                     const bool act = i < n && (k == 0 || G == 32);
                     s += act ? expf(l[k] - mx) : 0.f;
@@ -249,20 +297,20 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 s = group_sum(s, G); s0 = group_sum(s0, G);
                 const float lse = mx + logf(s), lse0 = mx0 + logf(s0);
 #pragma unroll
-                for (int k = 0; k < kMaxSources / 32; ++k) {
+                for (int k = 0; k < NPL; ++k) {
                     const int i = ii + 32 * k;
                     const bool act = i < n && (k == 0 || G == 32) && t < BT;
                     if (act) {
                         const float pi = expf(l[k] - lse), p0 = expf(lcv[k] - lse0);
                         const float tc = lds_f32(c0_a + 4u * i) + mass * (pi - p0);
-                        sts_f32(wt + 4u * (uint32_t)(i * BT + t), tc - cb[k]);
+                        sts_f32(wt + 4u * (uint32_t)(i * BT + t), tc - cb[u][k]);
                         if (cg == 0 && tok_ok) {
                             p.TC[tok * n + i] = tc;
                             if (p.LG) p.LG[tok * n + i] = l[k];
                         }
                     }
                 }
-                if (ii == 0 && cg == 0 && tok_ok && t < BT && p.LSE) { p.LSE[tok] = lse; p.LSE0[tok] = lse0; }
+                if (ii == 0 && cg == 0 && tok_ok && p.LSE) { p.LSE[tok] = lse; p.LSE0[tok] = lse0; }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(sfull_a + 8u * buf);
@@ -271,18 +319,18 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 }
 
 template <typename T, int FR, int NCW>
-static cudaError_t launch_fwd(const CUtensorMap &tmV, const CUtensorMap &tmBase, const ReadFwdParams &p, int grid,
-                              cudaStream_t stream) {
+static cudaError_t launch_fwd(const CUtensorMap &tmV, const CUtensorMap &tmBase, const CUtensorMap &tmH0,
+                              const ReadFwdParams &p, int grid, cudaStream_t stream) {
     size_t smem = read_fwd_smem_bytes(FR, NCW, p.stages);
     cudaError_t e = cudaFuncSetAttribute(read_fwd_kernel<T, FR, NCW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    read_fwd_kernel<T, FR, NCW><<<grid, (NCW + 1 + kFwdScalarWarps) * 32, smem, stream>>>(tmV, tmBase, p);
+    read_fwd_kernel<T, FR, NCW><<<grid, (NCW + 1 + kFwdScalarWarps) * 32, smem, stream>>>(tmV, tmBase, tmH0, p);
     return cudaGetLastError();
 }
 
 cudaError_t launch_read_fwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmBase,
-                            const ReadFwdParams &p, int grid, cudaStream_t stream) {
-#define LB_FWD_CASE(TT, F, W) return launch_fwd<TT, F, W>(tmV, tmBase, p, grid, stream)
+                            const CUtensorMap &tmH0, const ReadFwdParams &p, int grid, cudaStream_t stream) {
+#define LB_FWD_CASE(TT, F, W) return launch_fwd<TT, F, W>(tmV, tmBase, tmH0, p, grid, stream)
 #define LB_FWD_FR(TT, W) \
     switch (fr) { case 1: LB_FWD_CASE(TT, 1, W); case 2: LB_FWD_CASE(TT, 2, W); case 3: LB_FWD_CASE(TT, 3, W); \
                   case 4: LB_FWD_CASE(TT, 4, W); default: break; }

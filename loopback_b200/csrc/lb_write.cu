@@ -184,7 +184,7 @@ cudaError_t launch_write(int dtype, const WriteParams &p, int sms, cudaStream_t 
     if (p.nq > 128) return cudaErrorInvalidValue;
     // two tokens per lane halve the shared-memory traffic per score; one token per lane gives twice the CTAs
     // (better balance when the tiles do not fill the SMs several times over)
-    const int tt = p.write_tt ? p.write_tt : (p.n_tok >= (long long)sms * 64 * 6 ? 2 : 1);
+    const int tt = p.write_tt ? p.write_tt : (p.n_tok >= (long long)sms * 64 * 3 ? 2 : 1);
     return dtype == LB_DTYPE_BF16 ? launch_write_d<__nv_bfloat16>(p, tt, stream) : launch_write_d<float>(p, tt, stream);
 }
 

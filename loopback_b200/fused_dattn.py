@@ -22,7 +22,8 @@ import torch
 from . import _lib
 from ._lib import check, dtype_code, ptr, stream_ptr
 
-__all__ = ["rstd", "fused_read_supported", "FusedDattnRead", "DattnStack", "_alias", "FusedDattnReadStk"]
+__all__ = ["rstd", "fused_read_supported", "FusedDattnRead", "DattnStack", "_alias", "FusedDattnReadStk",
+           "FusedCombineStk"]
 
 
 def _require_cuda(t: torch.Tensor, what: str) -> None:
@@ -400,6 +401,81 @@ class FusedDattnReadStk(torch.autograd.Function):
                  *[None] * n, *[_alias(stack.dR, i) if final[i] else None for i in range(n)])
         # Release the stack from this node: ctx attributes live as long as the graph node, and a training loop that
         # keeps each micro-batch's loss until the optimizer step would otherwise keep every micro-batch's stack.
+        ctx.stack = None
+        return grads
+
+
+class FusedCombineStk(torch.autograd.Function):
+    """(out, tc) = apply(stack, step, q, proposal, h0, beta, tc_prev, lam, c0, *updates, *scales).
+
+    FusedDattnReadStk with the cell's prologue folded into the kernels (LoopDeltaAttnRes.combine,
+    looped_transformer.py:380-391): the installed coefficients are lam * (tc_prev, 1) and, when h0 is given (the
+    read closes an iteration), base = proposal + beta (h0 - proposal). No base tensor, no coefficient tensor and
+    none of the small torch kernels that built them exist any more; results are those of the unfused sequence."""
+
+    @staticmethod
+    def forward(ctx, stack, step, q, proposal, h0, beta, tc_prev, lam, c0, *srcs):
+        n = len(srcs) // 2
+        d, n_tok, dev = stack.d, stack.n_tok, stack.V.device
+        for name, t in (("proposal", proposal), ("h0", h0)):
+            if t is not None and (t.dtype != stack.V.dtype or not t.is_contiguous() or t.shape[:-1] != stack.V.shape[1:3]):
+                raise RuntimeError(f"delta_attnres stacked read: {name} must be contiguous, the stack's dtype and shape")
+        if n < 2 or tc_prev is None or tc_prev.shape[-1] != n - 1:
+            raise RuntimeError("delta_attnres stacked read: the previous read's coefficients must have n - 1 entries")
+        qc = q.detach().float().contiguous()
+        c0c = c0.detach().float().contiguous()
+        tcp = tc_prev.detach().float().contiguous()
+        if stack.DOTS is not None and all(stack.r_done[:n]):
+            dots, qi = stack.DOTS, step - 1
+        else:
+            dots, qi = torch.empty((stack.n_steps, n_tok), device=dev, dtype=torch.float32), 0
+            with torch.cuda.device(dev):
+                check(_lib.lib().lb_scores(ptr(stack.V), ptr(qc), ptr(dots), n_tok, d, stack.n_steps, n,
+                                           dtype_code(stack.V.dtype), stream_ptr()), "scores")
+        save = any(ctx.needs_input_grad)
+        out = torch.empty_like(proposal)
+        tc = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
+        lg = lse = lse0 = None
+        if save:
+            lg = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
+            lse = torch.empty(n_tok, device=dev, dtype=torch.float32)
+            lse0 = torch.empty(n_tok, device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev), _timed("read_fwd", n):
+            check(_lib.lib().lb_combine_fwd(ptr(stack.V), ptr(stack.R), ptr(dots), int(qi), ptr(proposal.detach()),
+                                            ptr(None if h0 is None else h0.detach()), float(beta), ptr(tcp), float(lam),
+                                            ptr(c0c), ptr(out), ptr(tc), ptr(lg), ptr(lse), ptr(lse0), n_tok, d,
+                                            stack.n_steps, n, dtype_code(stack.V.dtype), stream_ptr()), "combine forward")
+        if save:
+            ctx.save_for_backward(qc, tcp, c0c, lg, lse, lse0)
+        ctx.stack, ctx.step, ctx.n, ctx.q_dtype, ctx.shape = stack, int(step), n, q.dtype, proposal.shape
+        ctx.lam, ctx.beta, ctx.blend = float(lam), float(beta), h0 is not None
+        ctx.finalize = bool(stack.fuse_final and save and ctx.needs_input_grad[9 + n + int(step)])
+        return out, tc.view(*proposal.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, g, gt):
+        qc, tcp, c0c, lg, lse, lse0 = ctx.saved_tensors
+        stack, step, n = ctx.stack, ctx.step, ctx.n
+        d, n_tok, dev = stack.d, stack.n_tok, stack.V.device
+        accum = stack.grads()
+        g = g.contiguous()
+        gt_c = None if gt is None else gt.reshape(n_tok, n).float().contiguous()
+        neg = None
+        if ctx.finalize:
+            neg = torch.empty(stack.V.shape[1:], device=dev, dtype=stack.V.dtype)
+            stack._scale_done[step], stack._neg[step] = True, neg
+        dtc = torch.empty((n_tok, n - 1), device=dev, dtype=torch.float32)
+        dq = torch.empty(d, device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev), _timed("read_bwd", n, accum):
+            check(_lib.lib().lb_combine_bwd(ptr(stack.V), ptr(stack.R), ptr(stack.dV), ptr(stack.dR), ptr(qc), ptr(g),
+                                            ptr(gt_c), ptr(tcp), ctx.lam, ptr(c0c), ptr(lg), ptr(lse), ptr(lse0),
+                                            ptr(dtc), ptr(dq), ptr(stack.scratch()), ptr(neg), int(ctx.finalize), n_tok,
+                                            d, stack.n_steps, n, int(bool(accum)), dtype_code(stack.V.dtype),
+                                            stream_ptr()), "combine backward")
+        dprop, dh0 = (g * (1.0 - ctx.beta), g * ctx.beta) if ctx.blend else (g, None)
+        final = [i == step or (step == 1 and i == 0) for i in range(n)]
+        grads = (None, None, dq.to(ctx.q_dtype), dprop, dh0, None, dtc.view(*ctx.shape[:-1], n - 1), None, None,
+                 *[None] * n, *[_alias(stack.dR, i) if final[i] else None for i in range(n)])
         ctx.stack = None
         return grads
 
