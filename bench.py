@@ -192,6 +192,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on small cases)")
     ap.add_argument("--opt", action="append", default=[], help="library tuning knob name=value (lb_set_option)")
+    ap.add_argument("--no-fuse-prologue", action="store_true", help="keep the cell's prologue in torch (A/B)")
     ap.add_argument("--detail", default="", help="write per-launch timings (kind, n, GB/s) to this file")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
@@ -226,6 +227,7 @@ def main():
     n_tok = w["b"] * w["t"]
     elem = 2 if w["dtype"] == "bf16" else 4
     P = Pass(w, dev, seed=rank)
+    P.cell.fuse_prologue = not args.no_fuse_prologue
 
     def barrier():
         if world > 1:

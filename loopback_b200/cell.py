@@ -31,6 +31,7 @@ class LoopDeltaAttnRes(nn.Module):
         self.beta = float(beta)
         self.eps = float(eps)
         self.query = nn.Parameter(torch.zeros(self.num_steps - 1, self.dim))
+        self.fuse_prologue = True      # fold the boundary blend and the coefficient append/decay into the kernels
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -82,7 +83,7 @@ class LoopDeltaAttnRes(nn.Module):
             raise ValueError(f"delta_attnres step {step} received {len(deltas)} deltas, expected {step + 1}")
 
         closes_iteration = block_idx == self.num_blocks - 1
-        if stack is not None and step >= 1 and coeffs is not None and proposal.is_contiguous() \
+        if self.fuse_prologue and stack is not None and step >= 1 and coeffs is not None and proposal.is_contiguous() \
                 and (not closes_iteration or h0.is_contiguous()):
             rows = self.prior_rows(proposal.device)
             if prior_coeffs is not None and prior_coeffs.data_ptr() == rows[step - 1].data_ptr():

@@ -311,40 +311,49 @@ static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int q
     const int nch = chunks_of(d, dtype);
     const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
     const bool rank4 = !g_opt.tma_per_chunk && (d * elem) % lb::kChunkBytes == 0;
-    // a row of at most 4 chunks is one warp's work (8 tokens x the whole row per tile); wider rows are cut into
-    // column groups of 2 chunks over 16-token tiles; few tokens: the smaller tile, for more CTAs
-    int ncw = g_opt.fwd_warps == 8 || g_opt.fwd_warps == 16 ? g_opt.fwd_warps : (nch <= 4 ? 8 : 16);
-    if (n_tok <= 8 * (long long)di.sms && g_opt.fwd_warps == 0) ncw = 8;
-    const long long tok_tiles = (n_tok + ncw - 1) / ncw;
-    // fragments per warp: the widest tile that wastes no shared memory, narrowed until the grid fills the GPU
-    int fr = g_opt.fwd_fr;
-    if (fr < 1 || fr > 4) {
-        int best = 1, best_waste = 1 << 30;
-        const int fmax = ncw == 16 ? 2 : 4;
-        for (int f = fmax; f >= 1; --f) {
-            const int cgs = (nch + f - 1) / f;
-            const int waste = cgs * f - nch;
-            if (waste < best_waste) { best_waste = waste; best = f; }
+    // Tile shape: consumer warps (16, 12 or 8), warps per token and fragments per warp. A tile normally spans the
+    // whole row (one column group); the choice avoids idle fragments first, then prefers stages near 16 KiB.
+    // With too few tokens to give every SM a tile, the row is cut into column groups instead (8-token tiles).
+    int ncw = 0, wpt = 0, fr = 0, best_cost = 1 << 30;
+    static const int kNcw[3] = {8, 12, 16};
+    for (int a = 0; a < 3; ++a) {
+        if (g_opt.fwd_warps && g_opt.fwd_warps != kNcw[a]) continue;
+        for (int w = 1; w <= kNcw[a]; ++w) {
+            if (kNcw[a] % w) continue;
+            const int f = (nch + w - 1) / w;
+            if (f > 4 || (g_opt.fwd_fr && g_opt.fwd_fr != f)) continue;
+            const int stage_kb = nch * (kNcw[a] / w) / 2;
+            const int off = stage_kb > 16 ? stage_kb - 16 : 16 - stage_kb;
+            const int cost = (f * w - nch) * 64 + off * 2 + a;
+            if (cost < best_cost) { best_cost = cost; ncw = kNcw[a]; wpt = w; fr = f; }
         }
-        fr = best;
-        while (fr > 1 && tok_tiles * ((nch + fr - 1) / fr) < di.sms) --fr;
     }
-    const int cg = (nch + fr - 1) / fr;
+    if (ncw == 0) return fail(LB_ERR_UNSUPPORTED, "lb_read_fwd: no tile shape covers d=%d (row of %d chunks)", d, nch);
+    int bt = ncw / wpt;
+    long long tok_tiles = (n_tok + bt - 1) / bt;
+    int cg = 1;
+    if (tok_tiles < di.sms) {            // few tokens: 8 tokens x (fr chunks) tiles, as many column groups as it takes
+        ncw = 8; wpt = 1; bt = 8;
+        tok_tiles = (n_tok + 7) / 8;
+        fr = nch < 4 ? nch : 4;
+        while (fr > 1 && tok_tiles * ((nch + fr - 1) / fr) < di.sms) --fr;
+        cg = (nch + fr - 1) / fr;
+    }
     int stages = g_opt.fwd_stages > 0 ? g_opt.fwd_stages : 8;
     if (stages > 12) stages = 12;
     while (stages > 2 && lb::read_fwd_smem_bytes(fr, ncw, stages) > kMaxSmem) --stages;
 
     CUtensorMap tmV, tmB, tmH;
-    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, ncw, rank4 ? fr : 0))) return rc;
-    if ((rc = make_map(&tmB, base, dtype, n_tok, d, 0, ncw, rank4 ? fr : 0))) return rc;
-    if ((rc = make_map(&tmH, h0 ? h0 : base, dtype, n_tok, d, 0, ncw, rank4 ? fr : 0))) return rc;
+    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, bt, rank4 ? fr * wpt : 0))) return rc;
+    if ((rc = make_map(&tmB, base, dtype, n_tok, d, 0, bt, rank4 ? fr * wpt : 0))) return rc;
+    if ((rc = make_map(&tmH, h0 ? h0 : base, dtype, n_tok, d, 0, bt, rank4 ? fr * wpt : 0))) return rc;
 
     lb::ReadFwdParams p;
     p.R = R;
     p.dots = DOTS + (long long)qi * N * n_tok;
     p.cbar = cbar; p.tc_prev = tc_prev; p.lam = lam; p.blend = h0 ? 1 : 0; p.beta = beta;
     p.c0 = c0; p.out = out; p.TC = TC; p.LG = LG; p.LSE = LSE; p.LSE0 = LSE0;
-    p.n_tok = n_tok; p.d = d; p.n = n; p.chunks = nch; p.col_groups = cg; p.tok_tiles = tok_tiles;
+    p.n_tok = n_tok; p.d = d; p.n = n; p.chunks = nch; p.wpt = wpt; p.col_groups = cg; p.tok_tiles = tok_tiles;
     p.stages = stages;
     p.rank4 = rank4 ? 1 : 0;
     p.inv_sqrt_d = 1.0f / sqrtf((float)d);

@@ -110,11 +110,15 @@ struct WaitCtx {
     int *err_word;              // global memory, per device
 };
 
+// `relaxed` waits (the scalar warps': they run a tile ahead of the consumers) sleep between polls, so
+// that their polling does not take issue slots from the consumer warps on the same scheduler.
+template <bool kRelaxed = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx &wc, int what) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
+        if (kRelaxed) __nanosleep(128);
         if ((++spins & 255u) == 0u) {
             if (lds_volatile_s32(wc.abort_flag)) return false;
             if (clock64() - t0 > kWaitCycles) {

@@ -29,7 +29,8 @@ struct ReadFwdParams {
     int d;
     int n;
     int chunks;            // ceil(d * elem / 512)
-    int col_groups;        // ceil(chunks / FR)
+    int wpt;               // consumer warps per token; tokens per tile = consumer warps / wpt
+    int col_groups;        // ceil(chunks / (FR * wpt))
     long long tok_tiles;   // ceil(n_tok / tokens per tile)
     int rank4;             // 1: one 4-D TMA box per stage (d a multiple of the chunk width), 0: one box per chunk
     int stages;

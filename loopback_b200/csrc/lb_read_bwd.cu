@@ -392,7 +392,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         int tcount = 0;
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
             const uint32_t buf = tcount & 1;
-            if (!mbar_wait(sempty_a + 8u * buf, (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
+            if (!mbar_wait<true>(sempty_a + 8u * buf, (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
                 return;
             const uint32_t tb = tables_a + buf * kBwdTables * tfl4;
             for (int idx = sw * 32 + lane; idx < BT * n; idx += kBwdScalarWarps * 32) {

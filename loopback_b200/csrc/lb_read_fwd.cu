@@ -6,10 +6,11 @@
 // Replaces the reference's stored-score read kernel (fused_dattn.py:588-625) and the host preparation around it
 // (fused_dattn.py:735-745: log-prior and mass are formed in the kernel from c0).
 //
-// One persistent CTA per SM walks tiles of NCW tokens x FR chunks (a chunk is 512 B of a row; NCW = 8 or 16).
-// Warp roles:
-//   NCW consumers  warp w owns token w of the tile; lane l owns fragment l of each chunk; fp32 accumulators held as
-//                  pairs (fma.rn.f32x2)
+// One persistent CTA per SM walks tiles of BT = NCW / WPT tokens x FR * WPT chunks (a chunk is 512 B of a row;
+// NCW = 8, 12 or 16 consumer warps, WPT of them share a token). Normally a tile spans the whole row; only when there
+// are too few tokens to fill the GPU is the row also cut into column groups. Warp roles:
+//   NCW consumers  warp w owns FR chunks of token w / WPT; lane l owns fragment l of each chunk; fp32 accumulators
+//                  held as pairs (fma.rn.f32x2)
 //   1 producer     one lane issues TMA tile loads (base tile, then V[0..n) tiles) into a ring of stages
 //   4 scalar warps per tile, the n-source softmaxes of its tokens -> coefficient table in shared memory (double
 //                  buffered, one tile ahead of the consumers), and the saved TC / LG / LSE / LSE0
@@ -49,8 +50,10 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     constexpr int VEC = S::kVec;
     constexpr int P = S::kPairs;
     constexpr int BW = kChunkBytes / S::kBytes;               // columns per chunk
-    constexpr int BT = NCW;                                    // one consumer warp per token of the tile
-    constexpr uint32_t kStageBytes = FR * BT * kChunkBytes;
+    constexpr uint32_t kStageBytes = FR * NCW * kChunkBytes;   // BT tokens x (FR * WPT) chunks
+    const int WPT = p.wpt;                                     // consumer warps per token
+    const int BT = NCW / WPT;                                  // tokens per tile
+    const int CPT = FR * WPT;                                  // chunks per tile (one column group)
 
     // shared-window addresses of the regions of the dynamic shared memory
     extern __shared__ uint8_t smem_raw[];
@@ -94,17 +97,18 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         int st = 0; uint32_t ph = 0;      // ring position: stage index and its phase parity
         int tcount = 0;
         bool alive = true;      // turned off by a wait that ran out: the warp then finishes its loops without waiting or storing
+        const int t = warp / WPT, part = warp - t * WPT;       // this warp's token of the tile and slice of its row
         uint32_t foff[FR];      // byte offset of this lane's fragment k inside a stage (token-major if one 4-D box fills it)
 #pragma unroll
         for (int k = 0; k < FR; ++k)
-            foff[k] = (uint32_t)((p.rank4 ? warp * FR + k : k * BT + warp) * 32 + lane) * 16u;
+            foff[k] = (uint32_t)((p.rank4 ? t * CPT + part * FR + k : (part * FR + k) * BT + t) * 32 + lane) * 16u;
         long long tt = blockIdx.x / cg_count;
         int cg = (int)(blockIdx.x - tt * cg_count);
         const long long tt_step = gridDim.x / cg_count;
         const int cg_step = (int)(gridDim.x - tt_step * cg_count);
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
-            const long long tok = tt * BT + warp;
-            const int chunk0 = cg * FR;
+            const long long tok = tt * BT + t;
+            const int chunk0 = cg * CPT + part * FR;
             const uint32_t buf = tcount & 1;
             float2 acc[FR][P];
             {   // item 0: the base tile
@@ -140,7 +144,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 if (++st == NS) { st = 0; ph ^= 1u; }
             }
             if (alive && !mbar_wait(sfull_a + 8u * buf, (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
-            uint32_t wa = wtab_a + buf * kWtabBytes + 4u * warp;
+            uint32_t wa = wtab_a + buf * kWtabBytes + 4u * t;
             for (int i = 0; i < n; ++i, wa += 4u * BT) {
                 if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
                 const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
@@ -187,15 +191,15 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 const long long tt = tile / cg_count;
                 const int cg = (int)(tile - tt * cg_count);
                 const int tok0 = (int)(tt * BT);
-                const int chunk0 = cg * FR;
-                const int nch = min(FR, p.chunks - chunk0);
+                const int chunk0 = cg * CPT;
+                const int nch = min(CPT, p.chunks - chunk0);
                 for (int item = first_item; item < n; ++item) {
                     if (!mbar_wait(empty_a + 8u * st, ph ^ 1u, wc, kDevWaitEmpty)) {
                         ok = false;
                         break;
                     }
                     const uint32_t sb = stages_a + (uint32_t)st * kStageBytes, fb = full_a + 8u * st;
-                    if (p.rank4) {          // one box: FR chunks x BT tokens (chunks past the row are zero-filled)
+                    if (p.rank4) {          // one box: CPT chunks x BT tokens (chunks past the row are zero-filled)
                         mbar_arrive_expect_tx(fb, kStageBytes);
                         if (item < 0) tma_load_3d(sb, (item == first_item) ? &tmBase : &tmH0, fb, 0, chunk0, tok0);
                         else tma_load_4d(sb, &tmV, fb, 0, chunk0, tok0, item);
@@ -236,12 +240,12 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             const long long tt = tile / cg_count;
             const int cg = (int)(tile - tt * cg_count);
             const uint32_t buf = tcount & 1;
-            if (!mbar_wait(sempty_a + 8u * buf, (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
+            if (!mbar_wait<true>(sempty_a + 8u * buf, (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
                 return;
             const uint32_t wt = wtab_a + buf * kWtabBytes;
             // This warp's passes over the tile (pass = sw, sw + 4, ...; TPP tokens per pass). All their global loads
             // are issued before any of them is used, so a tile costs one memory round trip, not one per pass.
-            constexpr int U = (BT + kFwdScalarWarps - 1) / kFwdScalarWarps;     // passes per warp when TPP == 1
+            constexpr int U = (NCW + kFwdScalarWarps - 1) / kFwdScalarWarps;    // passes per warp when TPP == 1, WPT == 1
             constexpr int NPL = kMaxSources / 32;
             float rr[U][NPL], dd[U][NPL], cb[U][NPL];
 #pragma unroll
@@ -335,9 +339,11 @@ cudaError_t launch_read_fwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, 
     switch (fr) { case 1: LB_FWD_CASE(TT, 1, W); case 2: LB_FWD_CASE(TT, 2, W); case 3: LB_FWD_CASE(TT, 3, W); \
                   case 4: LB_FWD_CASE(TT, 4, W); default: break; }
     if (dtype == LB_DTYPE_BF16) {
-        if (ncw == 16) { LB_FWD_FR(__nv_bfloat16, 16) } else if (ncw == 8) { LB_FWD_FR(__nv_bfloat16, 8) }
+        if (ncw == 16) { LB_FWD_FR(__nv_bfloat16, 16) } else if (ncw == 12) { LB_FWD_FR(__nv_bfloat16, 12) }
+        else if (ncw == 8) { LB_FWD_FR(__nv_bfloat16, 8) }
     } else {
-        if (ncw == 16) { LB_FWD_FR(float, 16) } else if (ncw == 8) { LB_FWD_FR(float, 8) }
+        if (ncw == 16) { LB_FWD_FR(float, 16) } else if (ncw == 12) { LB_FWD_FR(float, 12) }
+        else if (ncw == 8) { LB_FWD_FR(float, 8) }
     }
 #undef LB_FWD_FR
 #undef LB_FWD_CASE
