@@ -158,19 +158,23 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             }
             if (alive && !mbar_wait(sfull_a + 8u * buf, (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
 
-            // ---- phase 1: one pass over the sources, the accumulation of source i-1 overlapping the dot of i
+            // ---- phase 1: one pass over the sources, software-pipelined two deep: iteration i loads source i and starts
+            // the warp reduction of g . v_i; the reduced value is published to the token's other warps one iteration
+            // later and consumed (A, B accumulation of that source) two iterations later, so neither the shuffle chain
+            // nor the exchange barrier sits on an iteration's critical path
             float2 A[FR][P], B[FR][P];
-            uint4 vprev[FR];                      // the previous source's fragments, still packed
+            uint4 v1[FR], v2[FR];                 // packed fragments of sources i-1 and i-2
 #pragma unroll
             for (int k = 0; k < FR; ++k) {
-                vprev[k] = zero4;
+                v1[k] = zero4; v2[k] = zero4;
 #pragma unroll
                 for (int e = 0; e < P; ++e) { A[k][e] = make_float2(0.f, 0.f); B[k][e] = make_float2(0.f, 0.f); }
             }
-            float sacc = 0.f, dot_prev = 0.f;
-            for (int i = 0; i <= n; ++i) {
+            float sacc = 0.f, d1 = 0.f, d2 = 0.f;  // this warp's g . v of sources i-1 and i-2
+            for (int i = 0; i < n + 2; ++i) {
+                if (WPT > 1 && i >= 1 && i <= n && lane == 0) sts_f32(xch_a + 4u * (((i - 1) & 1) * kBwdMaxNcw + warp), d1);
                 uint4 raw[FR];
-                float dot = 0.f;
+                float dnew = 0.f;
                 if (i < n) {
                     if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
                     const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
@@ -190,15 +194,17 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                             d2b = __ffma2_rn(g2[k][e + 1], vf[e + 1], d2b);
                         }
                     }
-                    dot = warp_sum((d2a.x + d2b.x) + (d2a.y + d2b.y));
-                    if (WPT > 1 && lane == 0) sts_f32(xch_a + 4u * ((i & 1) * kBwdMaxNcw + warp), dot);
+                    dnew = warp_sum((d2a.x + d2b.x) + (d2a.y + d2b.y));
+                } else {
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) raw[k] = zero4;
                 }
-                if (i > 0) {
-                    const uint32_t j4 = (uint32_t)(i - 1) * BT4;
-                    float gd = dot_prev;
+                if (i >= 2) {
+                    const uint32_t j4 = (uint32_t)(i - 2) * BT4;
+                    float gd = d2;
                     if (WPT > 1) {
                         gd = 0.f;
-                        const uint32_t xa = xch_a + 4u * (((i - 1) & 1) * kBwdMaxNcw + t * WPT);
+                        const uint32_t xa = xch_a + 4u * (((i - 2) & 1) * kBwdMaxNcw + t * WPT);
                         for (int w2 = 0; w2 < WPT; ++w2) gd += lds_f32(xa + 4u * w2);
                     }
                     if (part == 0 && lane == 0) sts_f32(gk + j4, gd);
@@ -210,7 +216,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
                         float2 vf[P];
-                        S::unpack2(vprev[k], vf);
+                        S::unpack2(v2[k], vf);
 #pragma unroll
                         for (int e = 0; e < P; ++e) {
                             A[k][e] = __ffma2_rn(a2, vf[e], A[k][e]);
@@ -219,10 +225,10 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     }
                 }
                 if (WPT > 1) named_bar_sync(bar_id, bar_threads);
-                dot_prev = dot;
-                if (i < n) {                      // after the loop vprev still holds source n - 1 (used by phase 2)
+                if (i < n + 1) {                  // after the loop v2 still holds source n - 1 (used by phase 2)
+                    d2 = d1; d1 = dnew;
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) vprev[k] = raw[k];
+                    for (int k = 0; k < FR; ++k) { v2[k] = v1[k]; v1[k] = raw[k]; }
                 }
             }
             // ---- query-gradient partial of this thread's columns: private shared-memory slots
@@ -303,7 +309,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                         const float kf = lds_f32(fin_a + t4);
                         const float2 kf2 = make_float2(kf, kf);
                         float2 vf[P], kv[P];
-                        S::unpack2(vprev[k], vf);
+                        S::unpack2(v2[k], vf);
 #pragma unroll
                         for (int e = 0; e < P; ++e) kv[e] = __fmul2_rn(kf2, vf[e]);
                         res = S::accum(res, kv);
