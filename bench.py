@@ -192,6 +192,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on small cases)")
     ap.add_argument("--opt", action="append", default=[], help="library tuning knob name=value (lb_set_option)")
+    ap.add_argument("--no-graph", action="store_true", help="do not replay the pass as a CUDA graph for `value`")
     ap.add_argument("--no-fuse-prologue", action="store_true", help="keep the cell's prologue in torch (A/B)")
     ap.add_argument("--detail", default="", help="write per-launch timings (kind, n, GB/s) to this file")
     args = ap.parse_args()
@@ -277,7 +278,31 @@ def main():
     gpu_launches = (L.LAUNCHES["count"] - count0) // args.steps
     FD.LAUNCH_TIMER = None
     assert FD.device_error() == 0, "a kernel gave up a bounded wait"
-    ms_per_step = total_ms / args.steps
+    eager_ms_per_step = total_ms / args.steps
+    ms_per_step, launch_mode = eager_ms_per_step, "eager launches from Python"
+
+    # ---- the same pass captured once as a CUDA graph and replayed: removes the host's launch gaps ----------------
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                one_pass()                                   # allocator warm-up on the capture stream
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                one_pass()
+            for _ in range(3):
+                graph.replay()
+            assert FD.device_error() == 0
+            with ClockSampler(local) as clocks_g:
+                graph_ms = timed(graph.replay, args.steps) / args.steps
+            assert FD.device_error() == 0, "a kernel gave up a bounded wait"
+            if graph_ms < ms_per_step:
+                ms_per_step, launch_mode, clocks = graph_ms, "CUDA graph replay of the whole pass", clocks_g
+        except Exception as e:  # noqa: BLE001 -- capture is an optimisation of the launch path only
+            launch_mode = f"eager launches from Python (graph capture failed: {type(e).__name__})"
     value = world * n_tok / (ms_per_step * 1e-3)
 
     # ---- roofline of the dominant kernel: algorithmic bytes of its launches over their event time -------------
@@ -391,6 +416,7 @@ def main():
                        "tokens_per_gpu": n_tok, "l2": "inputs larger than L2 (the update stack alone is "
                                                      f"{N * n_tok * d * elem / 2**20:.0f} MiB per GPU)",
                        "parallelism": f"tokens x{world}" if world > 1 else "single GPU",
+                       "launch": launch_mode, "eager_ms_per_step": eager_ms_per_step,
                        "pass_algorithmic_gbs": pass_gbs, "pass_frac_of_peak": pass_gbs / peak, "kernels": kernels},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
             "clocks": clocks.summary(),
