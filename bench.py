@@ -281,28 +281,40 @@ def main():
     eager_ms_per_step = total_ms / args.steps
     ms_per_step, launch_mode = eager_ms_per_step, "eager launches from Python"
 
-    # ---- the same pass captured once as a CUDA graph and replayed: removes the host's launch gaps ----------------
+    # ---- the same pass captured once as a CUDA graph and replayed: removes the host's launch gaps. The capture holds
+    # this rank's kernels only; the query-gradient all-reduce stays an ordinary call after each replay, and the
+    # ranks agree (outside any capture) on whether every one of them captured successfully.
     if not args.no_graph:
+        graph = None
         try:
             side = torch.cuda.Stream(device=dev)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                one_pass()                                   # allocator warm-up on the capture stream
+                P.run()                                      # allocator warm-up on the capture stream
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                one_pass()
-            for _ in range(3):
+                P.run()
+        except Exception as e:  # noqa: BLE001 -- capture is an optimisation of the launch path only
+            graph = None
+            launch_mode = f"eager launches from Python (graph capture failed: {type(e).__name__})"
+        ok = torch.tensor([1 if graph is not None else 0], device=dev)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            def graph_pass():
                 graph.replay()
+                if w["backward"] and world > 1:
+                    dist.all_reduce(P.cell.query.grad)
+            for _ in range(3):
+                graph_pass()
             assert FD.device_error() == 0
             with ClockSampler(local) as clocks_g:
-                graph_ms = timed(graph.replay, args.steps) / args.steps
+                graph_ms = timed(graph_pass, args.steps) / args.steps
             assert FD.device_error() == 0, "a kernel gave up a bounded wait"
             if graph_ms < ms_per_step:
                 ms_per_step, launch_mode, clocks = graph_ms, "CUDA graph replay of the whole pass", clocks_g
-        except Exception as e:  # noqa: BLE001 -- capture is an optimisation of the launch path only
-            launch_mode = f"eager launches from Python (graph capture failed: {type(e).__name__})"
     value = world * n_tok / (ms_per_step * 1e-3)
 
     # ---- roofline of the dominant kernel: algorithmic bytes of its launches over their event time -------------
