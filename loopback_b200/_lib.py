@@ -10,7 +10,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libloopback_b200.so")
+# LOOPBACK_B200_LIB overrides the library file (for trying an experimental build without touching the package)
+LIB_PATH = os.environ.get("LOOPBACK_B200_LIB") or os.path.join(_HERE, "libloopback_b200.so")
 
 LB_DTYPE_F32 = 0
 LB_DTYPE_BF16 = 1

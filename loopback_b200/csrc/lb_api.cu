@@ -426,21 +426,26 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     const int nch = chunks_of(d, dtype);
     const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
     const bool rank4 = !g_opt.tma_per_chunk && (d * elem) % lb::kChunkBytes == 0;
-    // consumer warps (16, 12 or 8), warps per token and fragments per warp: no idle fragments first, then tiles of
-    // at least 12 KiB, then 2 fragments per warp, then more warps
+    // Tile shape. A row of at most 4 chunks goes to ONE warp per token (8 consumer warps, 8 tokens per tile): no
+    // exchange between warps and the most work per barrier wait. Wider rows are split over several warps per token:
+    // consumer warps (12, 16 or 8), warps per token and fragments per warp are chosen for no idle fragments first,
+    // then tiles of at least 12 KiB, then 2 fragments per warp.
     int ncw = 0, wpt = 0, fr = 0, best_cost = 1 << 30;
     static const int kNcw[3] = {12, 16, 8}, kFrMax[3] = {2, 2, 4};
-    for (int a = 0; a < 3; ++a) {
-        if (g_opt.bwd_warps && g_opt.bwd_warps != kNcw[a]) continue;
-        for (int w = 1; w <= kNcw[a]; ++w) {
-            if (kNcw[a] % w) continue;
-            if (w > 1 && kNcw[a] / w > 8) continue;          // named barriers 1..8: one per token of the tile
-            if (g_opt.bwd_wpt && g_opt.bwd_wpt != w) continue;
-            const int f = (nch + w - 1) / w;
-            if (f > kFrMax[a]) continue;
-            const int stage = nch * (kNcw[a] / w) * lb::kChunkBytes;
-            const int cost = (f * w - nch) * 64 + (stage < 12 * 1024 ? 16 : 0) + (f == 2 ? 0 : (f == 3 ? 2 : (f == 1 ? 3 : 4))) * 2 + a;
-            if (cost < best_cost) { best_cost = cost; ncw = kNcw[a]; wpt = w; fr = f; }
+    if (nch <= 4 && g_opt.bwd_wpt <= 1 && (g_opt.bwd_warps == 0 || g_opt.bwd_warps == 8)) {
+        ncw = 8; wpt = 1; fr = nch;
+    } else {
+        for (int a = 0; a < 3; ++a) {
+            if (g_opt.bwd_warps && g_opt.bwd_warps != kNcw[a]) continue;
+            for (int w = 2; w <= kNcw[a]; ++w) {
+                if (kNcw[a] % w || kNcw[a] / w > 8) continue;     // named barriers 1..8: one per token of the tile
+                if (g_opt.bwd_wpt && g_opt.bwd_wpt != w) continue;
+                const int f = (nch + w - 1) / w;
+                if (f > kFrMax[a]) continue;
+                const int stage = nch * (kNcw[a] / w) * lb::kChunkBytes;
+                const int cost = (f * w - nch) * 64 + (stage < 12 * 1024 ? 16 : 0) + (f == 2 ? 0 : (f == 3 ? 2 : (f == 1 ? 3 : 4))) * 2 + a;
+                if (cost < best_cost) { best_cost = cost; ncw = kNcw[a]; wpt = w; fr = f; }
+            }
         }
     }
     if (ncw == 0) return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: no tile shape covers d=%d (row of %d chunks)", d, nch);

@@ -53,7 +53,9 @@ size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec)
     return 1024 + stages * stage + ((tables + 15) & ~size_t(15)) + slots + qrow + sizeof(BwdSmemTail) + 64;
 }
 
-template <typename T, int FR, int NCW>
+// SOLO: one warp owns a token's whole row (WPT == 1): no exchange between warps, no named barriers, a one-source-deep
+// pipeline; g stays packed in registers (unpacked where it is used) to leave room for 4 fragments per lane.
+template <typename T, int FR, int NCW, bool SOLO>
 __global__ void __launch_bounds__((NCW + 1 + kBwdScalarWarps) * 32, 1)
 read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
                 const __grid_constant__ CUtensorMap tmDV, ReadBwdParams p) {
@@ -66,7 +68,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     constexpr int kConsumerThreads = NCW * 32;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int NS = p.stages, n = p.n, WPT = p.wpt, BT = NCW / WPT;
+    const int NS = p.stages, n = p.n, WPT = SOLO ? 1 : p.wpt, BT = NCW / WPT;
     const uint32_t tfl4 = (uint32_t)bwd_table_floats(n, BT) * 4u;      // bytes of one table
 
     // shared-window addresses of the regions of the dynamic shared memory
@@ -146,12 +148,23 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             const uint32_t tb = tables_a + buf * kBwdTables * tfl4 + t4;
             const uint32_t gk = gdkq_a + t4;
             // ---- g tile -> registers (as fp32 pairs)
-            float2 g2[FR][P];
+            float2 g2[SOLO ? 1 : FR][P];
+            uint4 gpk[SOLO ? FR : 1];
+            auto load_g = [&](int k, float2 (&gf)[P]) {          // g fragment k as fp32 pairs
+                if constexpr (SOLO) S::unpack2(gpk[k], gf);
+                else {
+#pragma unroll
+                    for (int e = 0; e < P; ++e) gf[e] = g2[k][e];
+                }
+            };
             {
                 if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
                 const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
 #pragma unroll
-                for (int k = 0; k < FR; ++k) S::unpack2(valid[k] ? lds_v4(sb + foff[k]) : zero4, g2[k]);
+                for (int k = 0; k < FR; ++k) {
+                    const uint4 u = valid[k] ? lds_v4(sb + foff[k]) : zero4;
+                    if constexpr (SOLO) gpk[k] = u; else S::unpack2(u, g2[k]);
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_a + 8u * st);
                 if (++st == NS) { st = 0; ph ^= 1u; }
@@ -171,7 +184,8 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 for (int e = 0; e < P; ++e) { A[k][e] = make_float2(0.f, 0.f); B[k][e] = make_float2(0.f, 0.f); }
             }
             float sacc = 0.f, d1 = 0.f, d2 = 0.f;  // this warp's g . v of sources i-1 and i-2
-            for (int i = 0; i < n + 2; ++i) {
+            constexpr int DEPTH = SOLO ? 1 : 2;
+            for (int i = 0; i < n + DEPTH; ++i) {
                 if (WPT > 1 && i >= 1 && i <= n && lane == 0) sts_f32(xch_a + 4u * (((i - 1) & 1) * kBwdMaxNcw + warp), d1);
                 uint4 raw[FR];
                 float dnew = 0.f;
@@ -186,12 +200,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     float2 d2a = make_float2(0.f, 0.f), d2b = make_float2(0.f, 0.f);
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
-                        float2 vf[P];
+                        float2 vf[P], gf[P];
                         S::unpack2(raw[k], vf);
+                        load_g(k, gf);
 #pragma unroll
                         for (int e = 0; e < P; e += 2) {
-                            d2a = __ffma2_rn(g2[k][e], vf[e], d2a);
-                            d2b = __ffma2_rn(g2[k][e + 1], vf[e + 1], d2b);
+                            d2a = __ffma2_rn(gf[e], vf[e], d2a);
+                            d2b = __ffma2_rn(gf[e + 1], vf[e + 1], d2b);
                         }
                     }
                     dnew = warp_sum((d2a.x + d2b.x) + (d2a.y + d2b.y));
@@ -199,9 +214,9 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 #pragma unroll
                     for (int k = 0; k < FR; ++k) raw[k] = zero4;
                 }
-                if (i >= 2) {
-                    const uint32_t j4 = (uint32_t)(i - 2) * BT4;
-                    float gd = d2;
+                if (i >= DEPTH) {
+                    const uint32_t j4 = (uint32_t)(i - DEPTH) * BT4;
+                    float gd = SOLO ? d1 : d2;
                     if (WPT > 1) {
                         gd = 0.f;
                         const uint32_t xa = xch_a + 4u * (((i - 2) & 1) * kBwdMaxNcw + t * WPT);
@@ -216,7 +231,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
                         float2 vf[P];
-                        S::unpack2(v2[k], vf);
+                        S::unpack2(SOLO ? v1[k] : v2[k], vf);
 #pragma unroll
                         for (int e = 0; e < P; ++e) {
                             A[k][e] = __ffma2_rn(a2, vf[e], A[k][e]);
@@ -225,10 +240,10 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     }
                 }
                 if (WPT > 1) named_bar_sync(bar_id, bar_threads);
-                if (i < n + 1) {                  // after the loop v2 still holds source n - 1 (used by phase 2)
+                if (i < n + DEPTH - 1) {          // after the loop v2 (SOLO: v1) still holds source n - 1 (used by phase 2)
                     d2 = d1; d1 = dnew;
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) { v2[k] = v1[k]; v1[k] = raw[k]; }
+                    for (int k = 0; k < FR; ++k) { if constexpr (!SOLO) v2[k] = v1[k]; v1[k] = raw[k]; }
                 }
             }
             // ---- query-gradient partial of this thread's columns: private shared-memory slots
@@ -297,9 +312,10 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 }
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
-                    float2 o[P];
+                    float2 o[P], gf[P];
+                    load_g(k, gf);
 #pragma unroll
-                    for (int e = 0; e < P; ++e) o[e] = __ffma2_rn(w2, g2[k][e], __fmul2_rn(kq2, q2[k][e]));
+                    for (int e = 0; e < P; ++e) o[e] = __ffma2_rn(w2, gf[e], __fmul2_rn(kq2, q2[k][e]));
                     uint4 res = p.accum ? S::accum(prev[k], o) : S::pack2v(o);
                     const int col = (chunk0 + k) * BW + lane * VEC;
                     if (p.finalize && i == n - 1) {
@@ -309,7 +325,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                         const float kf = lds_f32(fin_a + t4);
                         const float2 kf2 = make_float2(kf, kf);
                         float2 vf[P], kv[P];
-                        S::unpack2(v2[k], vf);
+                        S::unpack2(SOLO ? v1[k] : v2[k], vf);
 #pragma unroll
                         for (int e = 0; e < P; ++e) kv[e] = __fmul2_rn(kf2, vf[e]);
                         res = S::accum(res, kv);
@@ -428,24 +444,27 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     }
 }
 
-template <typename T, int FR, int NCW>
+template <typename T, int FR, int NCW, bool SOLO>
 static cudaError_t launch_bwd(const CUtensorMap &tmV, const CUtensorMap &tmG, const CUtensorMap &tmDV,
                               const ReadBwdParams &p, int grid, cudaStream_t stream) {
     size_t smem = read_bwd_smem_bytes(FR, NCW, p.wpt, p.stages, p.n, Store<T>::kVec);
-    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR, NCW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR, NCW, SOLO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    read_bwd_kernel<T, FR, NCW><<<grid, (NCW + 1 + kBwdScalarWarps) * 32, smem, stream>>>(tmV, tmG, tmDV, p);
+    read_bwd_kernel<T, FR, NCW, SOLO><<<grid, (NCW + 1 + kBwdScalarWarps) * 32, smem, stream>>>(tmV, tmG, tmDV, p);
     return cudaGetLastError();
 }
 
 cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmG,
                             const CUtensorMap &tmDV, const ReadBwdParams &p, int grid, cudaStream_t stream) {
-    // instantiated shapes: 16 consumer warps x {1,2} fragments, 12 x {1,2}, 8 x {1,2,3,4}
-#define LB_BWD_CASE(TT, F, W) \
-    if (fr == F && ncw == W) return launch_bwd<TT, F, W>(tmV, tmG, tmDV, p, grid, stream);
-#define LB_BWD_ALL(TT)                                                                                   \
-    LB_BWD_CASE(TT, 1, 16) LB_BWD_CASE(TT, 2, 16) LB_BWD_CASE(TT, 1, 12) LB_BWD_CASE(TT, 2, 12)          \
-    LB_BWD_CASE(TT, 1, 8) LB_BWD_CASE(TT, 2, 8) LB_BWD_CASE(TT, 3, 8) LB_BWD_CASE(TT, 4, 8)
+    // instantiated shapes. Several warps per token: 16 consumer warps x {1,2} fragments, 12 x {1,2}, 8 x {1,2,3,4};
+    // one warp per token (SOLO): 8 x {1,2,3,4}
+#define LB_BWD_CASE(TT, F, W, SOLO_) \
+    if (fr == F && ncw == W && (p.wpt == 1) == SOLO_) return launch_bwd<TT, F, W, SOLO_>(tmV, tmG, tmDV, p, grid, stream);
+#define LB_BWD_ALL(TT)                                                                                         \
+    LB_BWD_CASE(TT, 1, 16, false) LB_BWD_CASE(TT, 2, 16, false) LB_BWD_CASE(TT, 1, 12, false)                   \
+    LB_BWD_CASE(TT, 2, 12, false) LB_BWD_CASE(TT, 1, 8, false) LB_BWD_CASE(TT, 2, 8, false)                     \
+    LB_BWD_CASE(TT, 3, 8, false) LB_BWD_CASE(TT, 4, 8, false) LB_BWD_CASE(TT, 1, 8, true) LB_BWD_CASE(TT, 2, 8, true) \
+    LB_BWD_CASE(TT, 3, 8, true) LB_BWD_CASE(TT, 4, 8, true)
     if (dtype == LB_DTYPE_BF16) { LB_BWD_ALL(__nv_bfloat16) } else { LB_BWD_ALL(float) }
 #undef LB_BWD_ALL
 #undef LB_BWD_CASE
