@@ -23,7 +23,7 @@ constexpr int kWrThreads = 128;
 constexpr int kWrChunkBytes = 128;
 
 template <typename T, int TT, int QPT>
-__global__ void __launch_bounds__(kWrThreads) write_kernel(WriteParams p) {
+__global__ void __launch_bounds__(kWrThreads, QPT > 12 ? 1 : (TT == 1 ? 8 : 4)) write_kernel(WriteParams p) {
     using S = Store<T>;
     constexpr int VEC = S::kVec;
     constexpr int KC = kWrChunkBytes / S::kBytes;         // columns per chunk
