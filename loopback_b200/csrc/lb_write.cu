@@ -155,6 +155,106 @@ __global__ void __launch_bounds__(kWrThreads, QPT > 12 ? 1 : (TT == 1 ? 8 : 4)) 
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// The same write for a handful of tokens (decode-style batches): one CTA per token, threads over the row, so that
+// even 64 tokens occupy 64 SMs and each streams the query block from L2 once. Queries are taken 32 at a time: every
+// thread keeps 32 partial dot products, a transposing shuffle reduction leaves query l's warp sum in lane l, and
+// the warps' sums meet in shared memory.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kWrSmallThreads = 256;
+constexpr int kWrSmallFrags = 4;          // fragments per thread: rows up to 256 * 4 * 16 bytes = 16 KiB
+
+__device__ __forceinline__ float transpose_reduce32(float (&vals)[32], int lane) {
+    // sum of vals[l] over all lanes, delivered to lane l (31 shuffles for 32 values)
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        const bool up = (lane & s) != 0;
+#pragma unroll
+        for (int k = 0; k < s; ++k) {
+            const float send = up ? vals[k] : vals[k + s];
+            const float keep = up ? vals[k + s] : vals[k];
+            vals[k] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+        }
+    }
+    return vals[0];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWrSmallThreads) write_small_kernel(WriteParams p) {
+    using S = Store<T>;
+    constexpr int VEC = S::kVec;
+    __shared__ float red[kWrSmallThreads / 32][kMaxSources];
+    __shared__ float ssred[kWrSmallThreads / 32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const long long tok = blockIdx.x;
+    const int d = p.d, nq = p.Q != nullptr ? p.nq : 0;
+    const T *h = static_cast<const T *>(p.h) + tok * d;
+    const T *x = static_cast<const T *>(p.x) + tok * d;
+    T *vout = static_cast<T *>(p.v) + tok * d;
+    float vf[kWrSmallFrags][VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int m = 0; m < kWrSmallFrags; ++m) {
+        const int col = (tid + kWrSmallThreads * m) * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) vf[m][e] = 0.f;
+        if (col < d) {
+            float hf[VEC], xf[VEC];
+            S::unpack(ld_global_stream_v4(h + col), hf);
+            S::unpack(ld_global_stream_v4(x + col), xf);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) vf[m][e] = hf[e] - xf[e];
+            const uint4 packed = S::pack(vf[m]);
+            S::unpack(packed, vf[m]);                                    // the stored (rounded) values
+            st_global_v4(vout + col, packed);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) ss = fmaf(vf[m][e], vf[m][e], ss);
+        }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) ssred[warp] = ss;
+    for (int jg = 0; jg < nq; jg += 32) {
+        float part[32];
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+            part[jj] = 0.f;
+            const int j = jg + jj;
+            if (j < nq) {
+                const float *qrow = p.Q + (long long)(p.j0 + j) * d;
+#pragma unroll
+                for (int m = 0; m < kWrSmallFrags; ++m) {
+                    const int col = (tid + kWrSmallThreads * m) * VEC;
+                    if (col < d) {
+#pragma unroll
+                        for (int e4 = 0; e4 < VEC / 4; ++e4) {
+                            const float4 q4 = __ldg(reinterpret_cast<const float4 *>(qrow + col) + e4);
+                            part[jj] = fmaf(vf[m][4 * e4], q4.x, part[jj]);
+                            part[jj] = fmaf(vf[m][4 * e4 + 1], q4.y, part[jj]);
+                            part[jj] = fmaf(vf[m][4 * e4 + 2], q4.z, part[jj]);
+                            part[jj] = fmaf(vf[m][4 * e4 + 3], q4.w, part[jj]);
+                        }
+                    }
+                }
+            }
+        }
+        const float tot = transpose_reduce32(part, lane);       // lane l: this warp's sum for query jg + l
+        if (jg + lane < nq) red[warp][jg + lane] = tot;
+    }
+    __syncthreads();
+    if (tid == 0 && p.r != nullptr) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWrSmallThreads / 32; ++w) t += ssred[w];
+        p.r[tok] = rsqrtf(t / (float)d + p.eps);
+    }
+    for (int j = tid; j < nq; j += kWrSmallThreads) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWrSmallThreads / 32; ++w) t += red[w][j];
+        p.dots_s[(long long)(p.j0 + j) * p.dots_qstride + tok] = t;
+    }
+}
+
 template <typename T, int TT, int QPT>
 static cudaError_t launch_write_t(const WriteParams &p, cudaStream_t stream) {
     constexpr int KC = kWrChunkBytes / Store<T>::kBytes;
@@ -182,6 +282,13 @@ static cudaError_t launch_write_d(const WriteParams &p, int tt, cudaStream_t str
 cudaError_t launch_write(int dtype, const WriteParams &p, int sms, cudaStream_t stream) {
     if (p.n_tok == 0) return cudaSuccess;
     if (p.nq > 128) return cudaErrorInvalidValue;
+    const int row_frags = p.d / (dtype == LB_DTYPE_BF16 ? 8 : 4);
+    if (p.write_tt == 0 && p.n_tok <= 4LL * sms && row_frags <= kWrSmallThreads * kWrSmallFrags) {
+        // a decode-sized batch: tiles of 32 tokens would leave most SMs idle
+        if (dtype == LB_DTYPE_BF16) write_small_kernel<__nv_bfloat16><<<(unsigned)p.n_tok, kWrSmallThreads, 0, stream>>>(p);
+        else write_small_kernel<float><<<(unsigned)p.n_tok, kWrSmallThreads, 0, stream>>>(p);
+        return cudaGetLastError();
+    }
     // two tokens per lane halve the shared-memory traffic per score; one token per lane gives twice the CTAs
     // (better balance when the tiles do not fill the SMs several times over)
     const int tt = p.write_tt ? p.write_tt : (p.n_tok >= (long long)sms * 64 * 3 ? 2 : 1);

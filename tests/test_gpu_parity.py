@@ -50,9 +50,12 @@ def cuda(x):
 # 1. the write, through the C ABI
 # ------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n_tok,d", [(5, 64), (37, 768), (130, 1024), (33, 1536), (9, 3072), (64, 2048)])
-def test_write_matches_oracle(L, dtype, n_tok, d):
-    N, NQ = 6, 5
+@pytest.mark.parametrize("tile", [0, 1, 2])      # 0: by size (one CTA per token for these batches); 1, 2: the tiled kernel
+@pytest.mark.parametrize("n_tok,d,N", [(5, 64, 6), (37, 768, 6), (130, 1024, 6), (33, 1536, 6), (9, 3072, 6),
+                                       (64, 2048, 6), (19, 512, 70)])
+def test_write_matches_oracle(L, dtype, n_tok, d, N, tile):
+    NQ = N - 1
+    L.set_option("write_tt", tile)
     g = torch.Generator().manual_seed(n_tok * 7 + d)
     x = torch.randn(n_tok, d, generator=g).to(dtype)
     Q = torch.randn(NQ, d, generator=g) * 0.3
@@ -69,6 +72,7 @@ def test_write_matches_oracle(L, dtype, n_tok, d):
         L.check(L.lib().lb_write(L.ptr(hc), L.ptr(xc), L.ptr(V), L.ptr(R), L.ptr(Qc), L.ptr(DOTS), n_tok, d, N, NQ, s,
                                  1e-6, code, L.stream_ptr()), "write")
     torch.cuda.synchronize()
+    L.set_option("write_tt", 0)
     for s in range(N):
         v_ref, r_ref = CO.write(hs[s].float().numpy(), x.float().numpy(), 1e-6, dtype == torch.bfloat16)
         assert torch.equal(V[s].float().cpu(), torch.from_numpy(v_ref)), "the stored update must be bit-exact"
