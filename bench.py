@@ -139,6 +139,11 @@ def run_reference_arm(args, w):
 # ------------------------------------------------------------------------------------------------------------------
 # the measured arm
 # ------------------------------------------------------------------------------------------------------------------
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured launches (d=1024, bf16, 8192
+# tokens; the summaries under profiles/ give the commands). Traffic grows in proportion to the tokens of a launch.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"read_bwd": 0.961, "read_fwd": 1.004, "write": 0.667}
+
+
 class Pass:
     """One K x R pass through the public entry points (DattnStack.write + LoopDeltaAttnRes.combine + autograd)."""
 
@@ -353,7 +358,11 @@ def main():
     if dominant:
         by, sec, cnt = per_kind[dominant]
         roofline = {"bound": "hbm", "kernel": dominant, "achieved": by / sec / 1e9, "peak": peak, "unit": "GB/s",
-                    "frac": by / sec / 1e9 / peak, "peak_source": peak_kind, "traffic": None,
+                    "frac": by / sec / 1e9 / peak, "peak_source": peak_kind,
+                    "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE[dominant] * by / cnt
+                                if w["d"] == 1024 and w["dtype"] == "bf16" else None),
+                    "traffic_source": "ncu dram bytes of an 8192-token capture of the same kernel and row size "
+                                      "(profiles/), scaled by tokens",
                     "bytes_per_launch_avg": by / cnt, "ms_per_launch_avg": sec * 1e3 / cnt}
     pass_units = algorithmic_units(N, w["backward"])
     pass_gbs = pass_units * n_tok * d * elem / (ms_per_step * 1e-3) / 1e9

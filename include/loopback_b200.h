@@ -56,8 +56,11 @@ const char *lb_last_error_string(void);
  * code of the first wait that ran out. SYNCHRONISES the device; meant for tests and for the end of a step. */
 int lb_device_error(int clear);
 
-/* Tuning knobs ("fwd_stages", "bwd_stages", "fwd_fr", "grid_cap"); value 0 restores the default.
- * Returns LB_ERR_ARG for an unknown name. */
+/* Tuning knobs for sweeps: "fwd_stages", "bwd_stages" (TMA ring depth), "fwd_fr" (chunks per consumer warp),
+ * "fwd_warps", "bwd_warps" (consumer warps per CTA: 8, 12 or 16), "bwd_wpt" (warps per token), "grid_cap" (CTAs),
+ * "tma_per_chunk" (one 3-D box per chunk instead of one 4-D box per stage), "write_tt" (tokens per lane of the tiled
+ * write kernel: 1 or 2, which also bypasses the per-token kernel for small batches). Value 0 restores the default
+ * (chosen by size). Returns LB_ERR_ARG for an unknown name. */
 int lb_set_option(const char *name, int value);
 
 /* Update write: V[s] = round(h - x); R[s] = key scale of the rounded update; if Q != NULL also the cached scores
