@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libloopback_b200.so")
-SOURCES = ("lb_api.cu", "lb_write.cu", "lb_read_fwd.cu", "lb_read_bwd.cu", "lb_noalloc.cu")
+SOURCES = ("lb_api.cu", "lb_write.cu", "lb_write_mma.cu", "lb_read_fwd.cu", "lb_read_bwd.cu", "lb_noalloc.cu")
 HEADERS = ("lb_common.cuh", "lb_kernels.h", os.path.join("..", "..", "include", "loopback_b200.h"))
 
 

@@ -126,6 +126,21 @@ int make_map(CUtensorMap *m, const void *base, int dtype, long long n_tok, int d
     return LB_OK;
 }
 
+// h / x of the tensor-core write: 2-D, boxes of box_tok rows x 64 bf16 columns, 128-byte swizzle
+int make_map_sw128(CUtensorMap *m, const void *base, long long n_tok, int d, int box_tok) {
+    auto fn = encode_fn();
+    if (!fn) return fail(LB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)n_tok};
+    cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_tok};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return LB_OK;
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_common(long long n_tok, int d, int dtype) {
@@ -208,6 +223,28 @@ int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, fl
     p.dots_s = DOTS ? DOTS + (long long)s * n_tok : nullptr;
     p.dots_qstride = (long long)N * n_tok;
     p.n_tok = n_tok; p.d = d; p.eps = eps; p.write_tt = g_opt.write_tt == 1 || g_opt.write_tt == 2 ? g_opt.write_tt : 0;
+    // bf16 rows in training-sized batches (every SM gets at least 32 tokens): the persistent tensor-core kernel
+    const int nt = lb::write_mma_ntiles(p.nq);
+    if (dtype == LB_DTYPE_BF16 && d >= 64 && nt >= 0 && n_tok > 0 &&
+        (g_opt.write_tt == 3 || (g_opt.write_tt == 0 && n_tok >= 32LL * di.sms))) {
+        const long long blocks32 = (n_tok + 31) / 32;
+        const long long rounds = (blocks32 + 8LL * di.sms - 1) / (8LL * di.sms);
+        const long long per = (blocks32 + di.sms * rounds - 1) / (di.sms * rounds);        // 1..8
+        lb::WriteMmaParams mp;
+        static_cast<lb::WriteParams &>(mp) = p;
+        mp.tile_tok = (int)per * 32;
+        mp.chunks = (d + 63) / 64;
+        mp.n_tiles = (n_tok + mp.tile_tok - 1) / mp.tile_tok;
+        mp.err_word = di.err_word;
+        mp.stages = 4;
+        while (mp.stages > 2 && lb::write_mma_smem_bytes(nt, mp.tile_tok, mp.stages) > 227 * 1024) --mp.stages;
+        CUtensorMap tmH, tmX;
+        if ((rc = make_map_sw128(&tmH, h, n_tok, d, mp.tile_tok))) return rc;
+        if ((rc = make_map_sw128(&tmX, x, n_tok, d, mp.tile_tok))) return rc;
+        const int grid = (int)(mp.n_tiles < di.sms ? mp.n_tiles : di.sms);
+        cudaError_t e = lb::launch_write_mma(tmH, tmX, mp, nt, grid, static_cast<cudaStream_t>(stream));
+        return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_write launch");
+    }
     cudaError_t e = lb::launch_write(dtype, p, di.sms, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_write launch");
 }

@@ -1,0 +1,339 @@
+// Update write for training-sized batches of bf16 rows (sm_100a): persistent, TMA-fed, scores on the tensor cores.
+//
+// Replaces the reference's _write_stk_kernel (fused_dattn.py:561-585) where the batch is large enough to give every
+// SM a tile of its own:  V[s] = round(h - x),  R[s] = rsqrt(mean(V[s]^2) + eps),  DOTS[j][s][t] = q_j . V[s][t]
+// for the queries j0 <= j < j0 + nq whose reads will see update s.
+//
+// The scores are the one contraction on the whole path ([tokens x d] . [d x nq]); on the fp32 pipes they cost more
+// issue slots than the row traffic leaves room for. Here they run as bf16 mma with fp32 accumulation, the fp32 query
+// split into three bf16 terms (q = hi + mid + lo, 24 mantissa bits in all), so every product is exact and the sums
+// are fp32 as in the reference.
+//
+// One CTA per SM; a CTA owns tiles of up to 256 consecutive tokens and walks each tile's rows in chunks of 64 columns:
+//   * one producer lane fills a ring of stages with the tile's h and x chunk (two TMA boxes of tile_tok x 128 bytes,
+//     128-byte swizzle so that both the 16-byte row accesses and ldmatrix are conflict-free);
+//   * two query warps convert the next chunk of the nq queries into the three bf16 terms (same swizzle), double-buffered;
+//   * 8 consumer warps own 32 tokens each. Per chunk a warp subtracts and rounds its rows (16 bytes per lane, coalesced
+//     store of V), writes the rounded values back into the stage, and feeds them to the tensor cores as the A operand
+//     (two 16-token tiles per warp); accumulators stay in registers across the whole row. No CTA-wide barrier.
+// Waits are bounded (lb_common.cuh); a CTA that gives up unwinds and reports through the device error word.
+#include "lb_common.cuh"
+#include "lb_kernels.h"
+
+namespace lb {
+
+constexpr int kWmConsumers = 8;                          // consumer warps; 32 tokens each
+constexpr int kWmQueryWarps = 2;
+constexpr int kWmThreads = (kWmConsumers + 1 + kWmQueryWarps) * 32;      // + producer warp + query warps
+constexpr int kWmKC = 64;                                // columns per chunk
+constexpr int kWmRow = 128;                              // bytes per token and chunk (one swizzle span)
+constexpr int kWmEpPitch = 33;                           // floats per query row of a warp's transposing buffer
+
+__device__ __forceinline__ void sts_v4(uint32_t a, const uint4 &v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts_v2(uint32_t a, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t a, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t a, uint32_t (&r)[2]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a) : "memory");
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// q = hi + mid + lo with three bf16 terms: each remainder is exact in fp32, the third term carries bits 17..24
+__device__ __forceinline__ void split3(float q, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(q);
+    const float r1 = q - __bfloat162float(h);
+    const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(m);
+    const __nv_bfloat16 l = __float2bfloat16_rn(r2);
+    hi = __bfloat16_as_ushort(h); mid = __bfloat16_as_ushort(m); lo = __bfloat16_as_ushort(l);
+}
+
+struct WmBars {
+    unsigned long long full[4], empty[4], qfull[2], qempty[2];
+    int abort_flag;
+};
+
+// Dynamic shared memory, from a 1024-byte boundary: stages x (h tile | x tile), 2 x 3 query-term blocks of NT x 1024
+// bytes, 8 transposing buffers, the barriers.
+template <int NT>
+__global__ void __launch_bounds__(kWmThreads, 1)
+write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant__ CUtensorMap tmX, WriteMmaParams p) {
+    using S = Store<__nv_bfloat16>;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t stages_a = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t tile_bytes = (uint32_t)p.tile_tok * kWmRow;
+    const uint32_t stage_bytes = 2u * tile_bytes;
+    constexpr uint32_t kQTerm = (NT > 0 ? NT : 1) * 1024u;          // one bf16 term of one chunk: NT * 8 rows x 128 B
+    const uint32_t qs_a = stages_a + (uint32_t)p.stages * stage_bytes;
+    const uint32_t ep_a = qs_a + 6u * kQTerm;
+    const uint32_t bars_a = ep_a + kWmConsumers * 8u * kWmEpPitch * 4u;
+    const uint32_t full_a = bars_a + offsetof(WmBars, full), empty_a = bars_a + offsetof(WmBars, empty);
+    const uint32_t qfull_a = bars_a + offsetof(WmBars, qfull), qempty_a = bars_a + offsetof(WmBars, qempty);
+    const uint32_t abort_a = bars_a + offsetof(WmBars, abort_flag);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NS = p.stages;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(full_a + 8u * s, 1); mbar_init(empty_a + 8u * s, kWmConsumers); }
+        for (int b = 0; b < 2; ++b) { mbar_init(qfull_a + 8u * b, 32 * kWmQueryWarps); mbar_init(qempty_a + 8u * b, kWmConsumers); }
+        sts_s32(abort_a, 0);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const WaitCtx wc{abort_a, p.err_word};
+    const int chunks = p.chunks;
+    const int nq = NT > 0 ? p.nq : 0;
+
+    if (warp < kWmConsumers) {
+        // ------------------------------------------------------------------ consumers
+        const int row0 = warp * 32;
+        const bool active = row0 < p.tile_tok;           // tiles are whole multiples of 32 tokens
+        const uint32_t my_ep = ep_a + (uint32_t)warp * 8u * kWmEpPitch * 4u;
+        const int g = lane >> 2, t4 = lane & 3;
+        // phase A: iteration i handles row row0 + 4 i + (lane / 8), fragment lane % 8
+        const int ar = lane >> 3, af = lane & 7;
+        // ldmatrix row addresses. A: matrix m = lane / 8 -> rows +8 (m & 1), k half (m >> 1).  B: lanes 0-15.
+        const uint32_t a_row = (uint32_t)(row0 + (lane & 7) + 8 * ((lane >> 3) & 1));
+        const uint32_t a_half = (uint32_t)(lane >> 4);
+        const uint32_t b_half = (uint32_t)((lane >> 3) & 1);
+        int st = 0; uint32_t ph = 0;
+        int qb = 0; uint32_t qph = 0;
+        bool alive = true;
+        for (long long tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
+            const long long tok0 = tile * p.tile_tok;
+            float acc[2][NT > 0 ? NT : 1][4];
+            float ss[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss[i] = 0.f;
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                for (int nt = 0; nt < (NT > 0 ? NT : 1); ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[mi][nt][e] = 0.f;
+            for (int c = 0; c < chunks; ++c) {
+                if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                if (NT > 0 && alive && !mbar_wait(qfull_a + 8u * qb, qph, wc, kDevWaitScalars)) alive = false;
+                const uint32_t sh = stages_a + (uint32_t)st * stage_bytes, sx = sh + tile_bytes;
+                if (active && alive) {
+                    const int col = c * kWmKC + af * 8;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = row0 + 4 * i + ar;
+                        const uint32_t a = (uint32_t)r * kWmRow + (uint32_t)((af ^ (r & 7)) << 4);
+                        float hf[8], xf[8];
+                        S::unpack(lds_v4(sh + a), hf);
+                        S::unpack(lds_v4(sx + a), xf);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) hf[e] = hf[e] - xf[e];
+                        const uint4 packed = S::pack(hf);
+                        S::unpack(packed, hf);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) ss[i] = fmaf(hf[e], hf[e], ss[i]);
+                        sts_v4(sh + a, packed);
+                        const long long tok = tok0 + r;
+                        if (tok < p.n_tok && col < p.d)
+                            st_global_v4(static_cast<__nv_bfloat16 *>(p.v) + tok * p.d + col, packed);
+                    }
+                    __syncwarp();
+                    if (NT > 0) {
+                        // the chunk's 12 accumulation steps run in fresh tensor-core accumulators (small terms
+                        // first); the running sums are round-to-nearest fp32 adds
+                        const uint32_t qbase = qs_a + (uint32_t)qb * 3u * kQTerm;
+                        float part[2][NT > 0 ? NT : 1][4];
+#pragma unroll
+                        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) part[mi][nt][e] = 0.f;
+#pragma unroll
+                        for (int kk = 0; kk < kWmKC / 16; ++kk) {
+                            uint32_t afr[2][4];
+#pragma unroll
+                            for (int mi = 0; mi < 2; ++mi) {
+                                const uint32_t row = a_row + 16u * mi;
+                                ldmatrix_x4(sh + row * kWmRow + (((2u * kk + a_half) ^ (row & 7u)) << 4), afr[mi]);
+                            }
+#pragma unroll
+                            for (int sp = 2; sp >= 0; --sp) {
+#pragma unroll
+                                for (int nt = 0; nt < NT; ++nt) {
+                                    uint32_t bfr[2];
+                                    const uint32_t qrow = 8u * nt + (lane & 7u);
+                                    ldmatrix_x2(qbase + sp * kQTerm + qrow * kWmRow + (((2u * kk + b_half) ^ (qrow & 7u)) << 4), bfr);
+                                    mma_bf16(part[0][nt], afr[0], bfr);
+                                    mma_bf16(part[1][nt], afr[1], bfr);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) acc[mi][nt][e] += part[mi][nt][e];
+                    }
+                }
+                fence_async_smem();            // the rounded rows written into the stage precede the TMA that refills it
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(empty_a + 8u * st);
+                    if (NT > 0) mbar_arrive(qempty_a + 8u * qb);
+                }
+                if (++st == NS) { st = 0; ph ^= 1u; }
+                if (NT > 0) { if (++qb == 2) { qb = 0; qph ^= 1u; } }
+            }
+            if (active && alive) {
+                // key scales: 8 lanes hold the parts of one row
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float s = ss[i];
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    s += __shfl_xor_sync(0xffffffffu, s, 2);
+                    s += __shfl_xor_sync(0xffffffffu, s, 4);
+                    const long long tok = tok0 + row0 + 4 * i + ar;
+                    if (af == 0 && p.r != nullptr && tok < p.n_tok) p.r[tok] = rsqrtf(s / (float)p.d + p.eps);
+                }
+                if (NT > 0) {
+                    // scores: accumulator tiles -> [query][token] through shared memory, then 128-byte rows per query
+                    const long long tok = tok0 + row0 + lane;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                        for (int mi = 0; mi < 2; ++mi) {
+                            const uint32_t e0 = my_ep + (uint32_t)((2 * t4) * kWmEpPitch + 16 * mi + g) * 4u;
+                            sts_f32(e0, acc[mi][nt][0]);
+                            sts_f32(e0 + kWmEpPitch * 4u, acc[mi][nt][1]);
+                            sts_f32(e0 + 8u * 4u, acc[mi][nt][2]);
+                            sts_f32(e0 + (kWmEpPitch + 8u) * 4u, acc[mi][nt][3]);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int qq = 0; qq < 8; ++qq) {
+                            const int j = 8 * nt + qq;
+                            const float val = lds_f32(my_ep + (uint32_t)(qq * kWmEpPitch + lane) * 4u);
+                            if (j < nq && tok < p.n_tok) p.dots_s[(long long)(p.j0 + j) * p.dots_qstride + tok] = val;
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+        }
+    } else if (warp == kWmConsumers) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmH);
+            tma_prefetch_desc(&tmX);
+            int st = 0; uint32_t ph = 0;
+            int issued = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < p.n_tiles; tile += gridDim.x) {
+                const int tok0 = (int)(tile * p.tile_tok);
+                for (int c = 0; c < chunks; ++c) {
+                    if (!mbar_wait(empty_a + 8u * st, ph ^ 1u, wc, kDevWaitEmpty)) { ok = false; break; }
+                    const uint32_t sh = stages_a + (uint32_t)st * stage_bytes, fb = full_a + 8u * st;
+                    mbar_arrive_expect_tx(fb, stage_bytes);
+                    tma_load_2d(sh, &tmH, fb, c * kWmKC, tok0);
+                    tma_load_2d(sh + tile_bytes, &tmX, fb, c * kWmKC, tok0);
+                    ++issued;
+                    if (++st == NS) { st = 0; ph ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // unwinding: let the copies already issued land before the CTA's shared memory is released
+                long long t0 = clock64();
+                int ds = st; uint32_t dp = ph;
+                for (int k = 0; k < NS && k < issued; ++k) {
+                    if (--ds < 0) { ds = NS - 1; dp ^= 1u; }
+                    while (!mbar_try_wait(full_a + 8u * ds, dp)) {
+                        if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
+                    }
+                }
+            }
+        }
+    } else if (NT > 0) {
+        // ------------------------------------------------------------------ query warps
+        int qb = 0; uint32_t qph = 0;
+        constexpr int kIter = (NT > 0 ? NT : 1) * 8 * (kWmKC / 4) / (32 * kWmQueryWarps);       // float4 per lane and chunk
+        const int ql = (warp - kWmConsumers - 1) * 32 + lane;
+        for (long long tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
+            for (int c = 0; c < chunks; ++c) {
+                // all loads of the chunk first (one round trip to L2), rows past nq and columns past d are zero
+                float4 q4[kIter];
+#pragma unroll
+                for (int it = 0; it < kIter; ++it) {
+                    const int idx = ql + 32 * kWmQueryWarps * it;
+                    const int j = idx >> 4, col = c * kWmKC + 4 * (idx & 15);
+                    q4[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (j < nq && col < p.d) q4[it] = __ldg(reinterpret_cast<const float4 *>(p.Q + (long long)(p.j0 + j) * p.d + col));
+                }
+                if (!mbar_wait<true>(qempty_a + 8u * qb, qph ^ 1u, wc, kDevWaitScalarSlot)) return;
+                const uint32_t qbase = qs_a + (uint32_t)qb * 3u * kQTerm;
+#pragma unroll
+                for (int it = 0; it < kIter; ++it) {
+                    const int idx = ql + 32 * kWmQueryWarps * it;
+                    const int j = idx >> 4, u4 = idx & 15;
+                    uint32_t h0, m0, l0, h1, m1, l1, h2, m2, l2, h3, m3, l3;
+                    split3(q4[it].x, h0, m0, l0); split3(q4[it].y, h1, m1, l1);
+                    split3(q4[it].z, h2, m2, l2); split3(q4[it].w, h3, m3, l3);
+                    const uint32_t a = qbase + (uint32_t)j * kWmRow + (uint32_t)((((u4 >> 1) ^ (j & 7)) << 4) + (u4 & 1) * 8);
+                    sts_v2(a, h0 | (h1 << 16), h2 | (h3 << 16));
+                    sts_v2(a + kQTerm, m0 | (m1 << 16), m2 | (m3 << 16));
+                    sts_v2(a + 2u * kQTerm, l0 | (l1 << 16), l2 | (l3 << 16));
+                }
+                mbar_arrive(qfull_a + 8u * qb);
+                if (++qb == 2) { qb = 0; qph ^= 1u; }
+            }
+        }
+    }
+}
+
+template <int NT>
+static cudaError_t launch_wm(const CUtensorMap &tmH, const CUtensorMap &tmX, const WriteMmaParams &p, int grid,
+                             size_t smem, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(write_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    write_mma_kernel<NT><<<grid, kWmThreads, smem, stream>>>(tmH, tmX, p);
+    return cudaGetLastError();
+}
+
+size_t write_mma_smem_bytes(int nt, int tile_tok, int stages) {
+    return 1024 + (size_t)stages * 2 * tile_tok * kWmRow + 6 * (size_t)(nt > 0 ? nt : 1) * 1024 +
+           (size_t)kWmConsumers * 8 * kWmEpPitch * 4 + sizeof(WmBars) + 64;
+}
+
+int write_mma_ntiles(int nq) {
+    const int need = (nq + 7) / 8;
+    const int have[] = {0, 1, 2, 3, 4};
+    for (int v : have)
+        if (need <= v) return v;
+    return -1;
+}
+
+cudaError_t launch_write_mma(const CUtensorMap &tmH, const CUtensorMap &tmX, const WriteMmaParams &p, int nt, int grid,
+                             cudaStream_t stream) {
+    const size_t smem = write_mma_smem_bytes(nt, p.tile_tok, p.stages);
+    switch (nt) {
+        case 0: return launch_wm<0>(tmH, tmX, p, grid, smem, stream);
+        case 1: return launch_wm<1>(tmH, tmX, p, grid, smem, stream);
+        case 2: return launch_wm<2>(tmH, tmX, p, grid, smem, stream);
+        case 3: return launch_wm<3>(tmH, tmX, p, grid, smem, stream);
+        case 4: return launch_wm<4>(tmH, tmX, p, grid, smem, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace lb

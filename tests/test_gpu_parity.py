@@ -50,9 +50,12 @@ def cuda(x):
 # 1. the write, through the C ABI
 # ------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tile", [0, 1, 2])      # 0: by size (one CTA per token for these batches); 1, 2: the tiled kernel
+# 0: by size (one CTA per token for small batches, the tensor-core kernel for large bf16 ones); 1, 2: the tiled kernel;
+# 3: the tensor-core kernel whatever the size (bf16 only; fp32 rows keep the choice by size)
+@pytest.mark.parametrize("tile", [0, 1, 2, 3])
 @pytest.mark.parametrize("n_tok,d,N", [(5, 64, 6), (37, 768, 6), (130, 1024, 6), (33, 1536, 6), (9, 3072, 6),
-                                       (64, 2048, 6), (19, 512, 70)])
+                                       (64, 2048, 6), (19, 512, 70), (5000, 320, 6), (40000, 136, 4),
+                                       (300, 4096, 3), (700, 1024, 40)])
 def test_write_matches_oracle(L, dtype, n_tok, d, N, tile):
     NQ = N - 1
     L.set_option("write_tt", tile)
