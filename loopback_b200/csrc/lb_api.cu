@@ -37,7 +37,7 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 struct Options {
     int fwd_stages = 0, bwd_stages = 0, fwd_fr = 0, grid_cap = 0, fwd_warps = 0, bwd_warps = 0, bwd_wpt = 0,
-        tma_per_chunk = 0, write_tt = 0;
+        tma_per_chunk = 0, write_tt = 0, write_mt = 0;
 } g_opt;
 
 struct DeviceInfo {
@@ -196,6 +196,7 @@ int lb_set_option(const char *name, int value) {
     else if (!strcmp(name, "bwd_wpt")) g_opt.bwd_wpt = value;
     else if (!strcmp(name, "tma_per_chunk")) g_opt.tma_per_chunk = value;
     else if (!strcmp(name, "write_tt")) g_opt.write_tt = value;
+    else if (!strcmp(name, "write_mt")) g_opt.write_mt = value;
     else return fail(LB_ERR_ARG, "unknown option '%s'", name);
     return LB_OK;
 }
@@ -242,7 +243,7 @@ int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, fl
         if ((rc = make_map_sw128(&tmH, h, n_tok, d, mp.tile_tok))) return rc;
         if ((rc = make_map_sw128(&tmX, x, n_tok, d, mp.tile_tok))) return rc;
         const int grid = (int)(mp.n_tiles < di.sms ? mp.n_tiles : di.sms);
-        cudaError_t e = lb::launch_write_mma(tmH, tmX, mp, nt, grid, static_cast<cudaStream_t>(stream));
+        cudaError_t e = lb::launch_write_mma(tmH, tmX, mp, nt, g_opt.write_mt == 1 ? 1 : 2, grid, static_cast<cudaStream_t>(stream));
         return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_write launch");
     }
     cudaError_t e = lb::launch_write(dtype, p, di.sms, static_cast<cudaStream_t>(stream));

@@ -72,8 +72,8 @@ struct WriteMmaParams : WriteParams {
 };
 int write_mma_ntiles(int nq);                                   // query tiles of 8 the kernel is built for, or -1
 size_t write_mma_smem_bytes(int nt, int tile_tok, int stages);
-cudaError_t launch_write_mma(const CUtensorMap &tmH, const CUtensorMap &tmX, const WriteMmaParams &p, int nt, int grid,
-                             cudaStream_t stream);
+cudaError_t launch_write_mma(const CUtensorMap &tmH, const CUtensorMap &tmX, const WriteMmaParams &p, int nt, int mt,
+                             int grid, cudaStream_t stream);   // mt: 16-token tiles per consumer warp (1 or 2)
 cudaError_t launch_rstd_fwd(int dtype, const void *x, float *r, long long n_tok, int d, float eps, int sms,
                             cudaStream_t stream);
 // mode 0: gx = gr (-r^3/d) x written;  mode 1: gx += round(gr (-r^3/d) x), rounded to the storage type

@@ -11,36 +11,28 @@
 //
 // One CTA per SM; a CTA owns tiles of up to 256 consecutive tokens and walks each tile's rows in chunks of 64 columns:
 //   * one producer lane fills a ring of stages with the tile's h and x chunk (two TMA boxes of tile_tok x 128 bytes,
-//     128-byte swizzle so that both the 16-byte row accesses and ldmatrix are conflict-free);
+//     128-byte swizzle so that the 16-byte accesses of 8 rows at one column are conflict-free);
 //   * two query warps convert the next chunk of the nq queries into the three bf16 terms (same swizzle), double-buffered;
-//   * 8 consumer warps own 32 tokens each. Per chunk a warp subtracts and rounds its rows (16 bytes per lane, coalesced
-//     store of V), writes the rounded values back into the stage, and feeds them to the tensor cores as the A operand
-//     (two 16-token tiles per warp); accumulators stay in registers across the whole row. No CTA-wide barrier.
+//   * 8 consumer warps own 32 tokens each (two 16-token mma tiles). Per chunk a lane reads 16-byte fragments of h and x
+//     in the mma operand arrangement, subtracts, rounds, stores V, and uses the rounded registers as the A operand as
+//     they are (no ldmatrix, nothing written back to shared memory); accumulators stay in registers across the whole
+//     row. No CTA-wide barrier.
 // Waits are bounded (lb_common.cuh); a CTA that gives up unwinds and reports through the device error word.
 #include "lb_common.cuh"
 #include "lb_kernels.h"
 
 namespace lb {
 
-constexpr int kWmConsumers = 8;                          // consumer warps; 32 tokens each
 constexpr int kWmQueryWarps = 2;
-constexpr int kWmThreads = (kWmConsumers + 1 + kWmQueryWarps) * 32;      // + producer warp + query warps
+// MT = 16-token mma tiles per consumer warp (1 or 2); 16 / MT consumer warps cover a tile of up to 256 tokens
+constexpr int wm_consumers(int mt) { return 16 / mt; }
+constexpr int wm_threads(int mt) { return (wm_consumers(mt) + 1 + kWmQueryWarps) * 32; }      // + producer + query warps
 constexpr int kWmKC = 64;                                // columns per chunk
 constexpr int kWmRow = 128;                              // bytes per token and chunk (one swizzle span)
 constexpr int kWmEpPitch = 33;                           // floats per query row of a warp's transposing buffer
 
-__device__ __forceinline__ void sts_v4(uint32_t a, const uint4 &v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 __device__ __forceinline__ void sts_v2(uint32_t a, uint32_t x, uint32_t y) {
     asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t a, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a) : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x2(uint32_t a, uint32_t (&r)[2]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a) : "memory");
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
@@ -48,7 +40,6 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // q = hi + mid + lo with three bf16 terms: each remainder is exact in fp32, the third term carries bits 17..24
 __device__ __forceinline__ void split3(float q, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
@@ -67,10 +58,12 @@ struct WmBars {
 
 // Dynamic shared memory, from a 1024-byte boundary: stages x (h tile | x tile), 2 x 3 query-term blocks of NT x 1024
 // bytes, 8 transposing buffers, the barriers.
-template <int NT>
-__global__ void __launch_bounds__(kWmThreads, 1)
+template <int NT, int MT>
+__global__ void __launch_bounds__(wm_threads(MT), 1)
 write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant__ CUtensorMap tmX, WriteMmaParams p) {
     using S = Store<__nv_bfloat16>;
+    constexpr int kWmConsumers = wm_consumers(MT);
+    constexpr int RW = 16 * MT;                 // rows per consumer warp
     extern __shared__ unsigned char smem_raw[];
     const uint32_t stages_a = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t tile_bytes = (uint32_t)p.tile_tok * kWmRow;
@@ -98,27 +91,21 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
 
     if (warp < kWmConsumers) {
         // ------------------------------------------------------------------ consumers
-        const int row0 = warp * 32;
+        const int row0 = warp * RW;
         const bool active = row0 < p.tile_tok;           // tiles are whole multiples of 32 tokens
         const uint32_t my_ep = ep_a + (uint32_t)warp * 8u * kWmEpPitch * 4u;
         const int g = lane >> 2, t4 = lane & 3;
-        // phase A: iteration i handles row row0 + 4 i + (lane / 8), fragment lane % 8
-        const int ar = lane >> 3, af = lane & 7;
-        // ldmatrix row addresses. A: matrix m = lane / 8 -> rows +8 (m & 1), k half (m >> 1).  B: lanes 0-15.
-        const uint32_t a_row = (uint32_t)(row0 + (lane & 7) + 8 * ((lane >> 3) & 1));
-        const uint32_t a_half = (uint32_t)(lane >> 4);
-        const uint32_t b_half = (uint32_t)((lane >> 3) & 1);
         int st = 0; uint32_t ph = 0;
         int qb = 0; uint32_t qph = 0;
         bool alive = true;
         for (long long tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
             const long long tok0 = tile * p.tile_tok;
-            float acc[2][NT > 0 ? NT : 1][4];
-            float ss[8];
+            float acc[MT][NT > 0 ? NT : 1][4];
+            float ss[2 * MT];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ss[i] = 0.f;
+            for (int i = 0; i < 2 * MT; ++i) ss[i] = 0.f;
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi)
+            for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
                 for (int nt = 0; nt < (NT > 0 ? NT : 1); ++nt)
 #pragma unroll
@@ -128,66 +115,72 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                 if (NT > 0 && alive && !mbar_wait(qfull_a + 8u * qb, qph, wc, kDevWaitScalars)) alive = false;
                 const uint32_t sh = stages_a + (uint32_t)st * stage_bytes, sx = sh + tile_bytes;
                 if (active && alive) {
-                    const int col = c * kWmKC + af * 8;
+                    // Both mma operands come straight from 16-byte shared-memory reads: lane (g, t4) owns fragment
+                    // t4 of a 32-column group for rows g and g + 8 of each 16-token tile. Its 8 columns feed two mma
+                    // steps (columns 0-3, then 4-7, as the k pairs {2 t4, 2 t4 + 1} and {2 t4 + 8, 2 t4 + 9}); the
+                    // query terms are read with the same pattern, so the two operands agree on which column is which k.
+                    float part[MT][NT > 0 ? NT : 1][4];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int r = row0 + 4 * i + ar;
-                        const uint32_t a = (uint32_t)r * kWmRow + (uint32_t)((af ^ (r & 7)) << 4);
-                        float hf[8], xf[8];
-                        S::unpack(lds_v4(sh + a), hf);
-                        S::unpack(lds_v4(sx + a), xf);
+                    for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) hf[e] = hf[e] - xf[e];
-                        const uint4 packed = S::pack(hf);
-                        S::unpack(packed, hf);
+                        for (int nt = 0; nt < (NT > 0 ? NT : 1); ++nt)
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) ss[i] = fmaf(hf[e], hf[e], ss[i]);
-                        sts_v4(sh + a, packed);
-                        const long long tok = tok0 + r;
-                        if (tok < p.n_tok && col < p.d)
-                            st_global_v4(static_cast<__nv_bfloat16 *>(p.v) + tok * p.d + col, packed);
-                    }
-                    __syncwarp();
-                    if (NT > 0) {
-                        // the chunk's 12 accumulation steps run in fresh tensor-core accumulators (small terms
-                        // first); the running sums are round-to-nearest fp32 adds
-                        const uint32_t qbase = qs_a + (uint32_t)qb * 3u * kQTerm;
-                        float part[2][NT > 0 ? NT : 1][4];
+                            for (int e = 0; e < 4; ++e) part[mi][nt][e] = 0.f;
+                    const uint32_t qbase = qs_a + (uint32_t)qb * 3u * kQTerm;
 #pragma unroll
-                        for (int mi = 0; mi < 2; ++mi)
+                    for (int grp = 0; grp < kWmKC / 32; ++grp) {
+                        const uint32_t unit = (uint32_t)(((4 * grp + t4) ^ g) << 4);      // swizzled; row & 7 == g
+                        const int col = c * kWmKC + grp * 32 + t4 * 8;
+                        uint32_t afr[2][MT][4];
 #pragma unroll
-                            for (int nt = 0; nt < NT; ++nt)
+                        for (int mi = 0; mi < MT; ++mi) {
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) part[mi][nt][e] = 0.f;
+                            for (int hh = 0; hh < 2; ++hh) {
+                                const int r = row0 + 16 * mi + 8 * hh + g;
+                                const uint32_t a = (uint32_t)r * kWmRow + unit;
+                                float hf[8], xf[8];
+                                S::unpack(lds_v4(sh + a), hf);
+                                S::unpack(lds_v4(sx + a), xf);
 #pragma unroll
-                        for (int kk = 0; kk < kWmKC / 16; ++kk) {
-                            uint32_t afr[2][4];
+                                for (int e = 0; e < 8; ++e) hf[e] = hf[e] - xf[e];
+                                const uint4 packed = S::pack(hf);
+                                S::unpack(packed, hf);
 #pragma unroll
-                            for (int mi = 0; mi < 2; ++mi) {
-                                const uint32_t row = a_row + 16u * mi;
-                                ldmatrix_x4(sh + row * kWmRow + (((2u * kk + a_half) ^ (row & 7u)) << 4), afr[mi]);
+                                for (int e = 0; e < 8; ++e) ss[2 * mi + hh] = fmaf(hf[e], hf[e], ss[2 * mi + hh]);
+                                const long long tok = tok0 + r;
+                                if (tok < p.n_tok && col < p.d)
+                                    st_global_v4(static_cast<__nv_bfloat16 *>(p.v) + tok * p.d + col, packed);
+                                afr[0][mi][hh] = packed.x; afr[0][mi][2 + hh] = packed.y;
+                                afr[1][mi][hh] = packed.z; afr[1][mi][2 + hh] = packed.w;
                             }
+                        }
+                        if (NT > 0) {
 #pragma unroll
-                            for (int sp = 2; sp >= 0; --sp) {
+                            for (int sp = 2; sp >= 0; --sp) {          // small terms first
 #pragma unroll
                                 for (int nt = 0; nt < NT; ++nt) {
-                                    uint32_t bfr[2];
-                                    const uint32_t qrow = 8u * nt + (lane & 7u);
-                                    ldmatrix_x2(qbase + sp * kQTerm + qrow * kWmRow + (((2u * kk + b_half) ^ (qrow & 7u)) << 4), bfr);
-                                    mma_bf16(part[0][nt], afr[0], bfr);
-                                    mma_bf16(part[1][nt], afr[1], bfr);
+                                    const uint4 b = lds_v4(qbase + sp * kQTerm + (uint32_t)(8 * nt + g) * kWmRow + unit);
+                                    const uint32_t b0[2] = {b.x, b.y}, b1[2] = {b.z, b.w};
+#pragma unroll
+                                    for (int mi = 0; mi < MT; ++mi) {
+                                        mma_bf16(part[mi][nt], afr[0][mi], b0);
+                                        mma_bf16(part[mi][nt], afr[1][mi], b1);
+                                    }
                                 }
                             }
                         }
+                    }
+                    // the chunk's 12 accumulation steps ran in fresh tensor-core accumulators; the running sums are
+                    // round-to-nearest fp32 adds
+                    if (NT > 0) {
 #pragma unroll
-                        for (int mi = 0; mi < 2; ++mi)
+                        for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
                             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) acc[mi][nt][e] += part[mi][nt][e];
                     }
                 }
-                fence_async_smem();            // the rounded rows written into the stage precede the TMA that refills it
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(empty_a + 8u * st);
@@ -197,15 +190,14 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                 if (NT > 0) { if (++qb == 2) { qb = 0; qph ^= 1u; } }
             }
             if (active && alive) {
-                // key scales: 8 lanes hold the parts of one row
+                // key scales: the 4 lanes of a row group hold the parts of rows g and g + 8 of each 16-token tile
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < 2 * MT; ++i) {
                     float s = ss[i];
                     s += __shfl_xor_sync(0xffffffffu, s, 1);
                     s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    s += __shfl_xor_sync(0xffffffffu, s, 4);
-                    const long long tok = tok0 + row0 + 4 * i + ar;
-                    if (af == 0 && p.r != nullptr && tok < p.n_tok) p.r[tok] = rsqrtf(s / (float)p.d + p.eps);
+                    const long long tok = tok0 + row0 + 16 * (i >> 1) + 8 * (i & 1) + g;
+                    if (t4 == 0 && p.r != nullptr && tok < p.n_tok) p.r[tok] = rsqrtf(s / (float)p.d + p.eps);
                 }
                 if (NT > 0) {
                     // scores: accumulator tiles -> [query][token] through shared memory, then 128-byte rows per query
@@ -213,7 +205,7 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-                        for (int mi = 0; mi < 2; ++mi) {
+                        for (int mi = 0; mi < MT; ++mi) {
                             const uint32_t e0 = my_ep + (uint32_t)((2 * t4) * kWmEpPitch + 16 * mi + g) * 4u;
                             sts_f32(e0, acc[mi][nt][0]);
                             sts_f32(e0 + kWmEpPitch * 4u, acc[mi][nt][1]);
@@ -225,7 +217,7 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                         for (int qq = 0; qq < 8; ++qq) {
                             const int j = 8 * nt + qq;
                             const float val = lds_f32(my_ep + (uint32_t)(qq * kWmEpPitch + lane) * 4u);
-                            if (j < nq && tok < p.n_tok) p.dots_s[(long long)(p.j0 + j) * p.dots_qstride + tok] = val;
+                            if (j < nq && lane < RW && tok < p.n_tok) p.dots_s[(long long)(p.j0 + j) * p.dots_qstride + tok] = val;
                         }
                         __syncwarp();
                     }
@@ -301,18 +293,18 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
     }
 }
 
-template <int NT>
+template <int NT, int MT>
 static cudaError_t launch_wm(const CUtensorMap &tmH, const CUtensorMap &tmX, const WriteMmaParams &p, int grid,
                              size_t smem, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(write_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(write_mma_kernel<NT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    write_mma_kernel<NT><<<grid, kWmThreads, smem, stream>>>(tmH, tmX, p);
+    write_mma_kernel<NT, MT><<<grid, wm_threads(MT), smem, stream>>>(tmH, tmX, p);
     return cudaGetLastError();
 }
 
 size_t write_mma_smem_bytes(int nt, int tile_tok, int stages) {
     return 1024 + (size_t)stages * 2 * tile_tok * kWmRow + 6 * (size_t)(nt > 0 ? nt : 1) * 1024 +
-           (size_t)kWmConsumers * 8 * kWmEpPitch * 4 + sizeof(WmBars) + 64;
+           (size_t)16 * 8 * kWmEpPitch * 4 + sizeof(WmBars) + 64;
 }
 
 int write_mma_ntiles(int nq) {
@@ -323,15 +315,15 @@ int write_mma_ntiles(int nq) {
     return -1;
 }
 
-cudaError_t launch_write_mma(const CUtensorMap &tmH, const CUtensorMap &tmX, const WriteMmaParams &p, int nt, int grid,
-                             cudaStream_t stream) {
+cudaError_t launch_write_mma(const CUtensorMap &tmH, const CUtensorMap &tmX, const WriteMmaParams &p, int nt, int mt,
+                             int grid, cudaStream_t stream) {
     const size_t smem = write_mma_smem_bytes(nt, p.tile_tok, p.stages);
     switch (nt) {
-        case 0: return launch_wm<0>(tmH, tmX, p, grid, smem, stream);
-        case 1: return launch_wm<1>(tmH, tmX, p, grid, smem, stream);
-        case 2: return launch_wm<2>(tmH, tmX, p, grid, smem, stream);
-        case 3: return launch_wm<3>(tmH, tmX, p, grid, smem, stream);
-        case 4: return launch_wm<4>(tmH, tmX, p, grid, smem, stream);
+        case 0: return mt == 1 ? launch_wm<0, 1>(tmH, tmX, p, grid, smem, stream) : launch_wm<0, 2>(tmH, tmX, p, grid, smem, stream);
+        case 1: return mt == 1 ? launch_wm<1, 1>(tmH, tmX, p, grid, smem, stream) : launch_wm<1, 2>(tmH, tmX, p, grid, smem, stream);
+        case 2: return mt == 1 ? launch_wm<2, 1>(tmH, tmX, p, grid, smem, stream) : launch_wm<2, 2>(tmH, tmX, p, grid, smem, stream);
+        case 3: return mt == 1 ? launch_wm<3, 1>(tmH, tmX, p, grid, smem, stream) : launch_wm<3, 2>(tmH, tmX, p, grid, smem, stream);
+        case 4: return mt == 1 ? launch_wm<4, 1>(tmH, tmX, p, grid, smem, stream) : launch_wm<4, 2>(tmH, tmX, p, grid, smem, stream);
         default: return cudaErrorInvalidValue;
     }
 }
