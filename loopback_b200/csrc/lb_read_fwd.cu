@@ -23,7 +23,7 @@
 namespace lb {
 
 constexpr int kFwdScalarWarps = 4;
-constexpr int kFwdMaxStages = 12;
+constexpr int kFwdMaxStages = 32;
 constexpr int kFwdMaxBT = 16;                     // tokens per tile == consumer warps (8 or 16)
 
 struct FwdSmemTail {

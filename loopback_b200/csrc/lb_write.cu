@@ -156,10 +156,11 @@ __global__ void __launch_bounds__(kWrThreads, QPT > 12 ? 1 : (TT == 1 ? 8 : 4)) 
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// The same write for a handful of tokens (decode-style batches): one CTA per token, threads over the row, so that
-// even 64 tokens occupy 64 SMs and each streams the query block from L2 once. Queries are taken 32 at a time: every
-// thread keeps 32 partial dot products, a transposing shuffle reduction leaves query l's warp sum in lane l, and
-// the warps' sums meet in shared memory.
+// The same write for a handful of tokens (decode-style batches): gridDim.y CTAs per token, threads over the row, so
+// that even 64 tokens occupy most SMs and the query block streams from L2 through all of them. Queries are taken 32 at
+// a time (group jg of a token goes to CTA jg mod gridDim.y; CTA 0 of the token also stores the update and its key
+// scale): every thread keeps 32 partial dot products, a transposing shuffle reduction leaves query l's warp sum in
+// lane l, and the warps' sums meet in shared memory.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kWrSmallThreads = 256;
 constexpr int kWrSmallFrags = 4;          // fragments per thread: rows up to 256 * 4 * 16 bytes = 16 KiB
@@ -206,14 +207,14 @@ __global__ void __launch_bounds__(kWrSmallThreads) write_small_kernel(WriteParam
             for (int e = 0; e < VEC; ++e) vf[m][e] = hf[e] - xf[e];
             const uint4 packed = S::pack(vf[m]);
             S::unpack(packed, vf[m]);                                    // the stored (rounded) values
-            st_global_v4(vout + col, packed);
+            if (blockIdx.y == 0) st_global_v4(vout + col, packed);
 #pragma unroll
             for (int e = 0; e < VEC; ++e) ss = fmaf(vf[m][e], vf[m][e], ss);
         }
     }
     ss = warp_sum(ss);
     if (lane == 0) ssred[warp] = ss;
-    for (int jg = 0; jg < nq; jg += 32) {
+    for (int jg = 32 * blockIdx.y; jg < nq; jg += 32 * gridDim.y) {
         float part[32];
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
@@ -241,13 +242,14 @@ __global__ void __launch_bounds__(kWrSmallThreads) write_small_kernel(WriteParam
         if (jg + lane < nq) red[warp][jg + lane] = tot;
     }
     __syncthreads();
-    if (tid == 0 && p.r != nullptr) {
+    if (tid == 0 && p.r != nullptr && blockIdx.y == 0) {
         float t = 0.f;
 #pragma unroll
         for (int w = 0; w < kWrSmallThreads / 32; ++w) t += ssred[w];
         p.r[tok] = rsqrtf(t / (float)d + p.eps);
     }
     for (int j = tid; j < nq; j += kWrSmallThreads) {
+        if ((j >> 5) % (int)gridDim.y != (int)blockIdx.y) continue;
         float t = 0.f;
 #pragma unroll
         for (int w = 0; w < kWrSmallThreads / 32; ++w) t += red[w][j];
@@ -285,8 +287,12 @@ cudaError_t launch_write(int dtype, const WriteParams &p, int sms, cudaStream_t 
     const int row_frags = p.d / (dtype == LB_DTYPE_BF16 ? 8 : 4);
     if (p.write_tt == 0 && p.n_tok <= 4LL * sms && row_frags <= kWrSmallThreads * kWrSmallFrags) {
         // a decode-sized batch: tiles of 32 tokens would leave most SMs idle
-        if (dtype == LB_DTYPE_BF16) write_small_kernel<__nv_bfloat16><<<(unsigned)p.n_tok, kWrSmallThreads, 0, stream>>>(p);
-        else write_small_kernel<float><<<(unsigned)p.n_tok, kWrSmallThreads, 0, stream>>>(p);
+        int qsplit = (int)(sms / p.n_tok), qgroups = (p.nq + 31) / 32;
+        if (qsplit > qgroups) qsplit = qgroups;
+        if (qsplit < 1) qsplit = 1;
+        const dim3 grid((unsigned)p.n_tok, (unsigned)qsplit);
+        if (dtype == LB_DTYPE_BF16) write_small_kernel<__nv_bfloat16><<<grid, kWrSmallThreads, 0, stream>>>(p);
+        else write_small_kernel<float><<<grid, kWrSmallThreads, 0, stream>>>(p);
         return cudaGetLastError();
     }
     // two tokens per lane halve the shared-memory traffic per score; one token per lane gives twice the CTAs
