@@ -67,6 +67,8 @@ int lb_set_option(const char *name, int value);
 /* Update write: V[s] = round(h - x); R[s] = key scale of the rounded update; if Q != NULL also the cached scores
  * DOTS[j][s][:] = Q[j] . V[s] for the queries j >= max(s - 1, 0) (the reads that will see update s).
  * R may be NULL (then only V[s] is written and Q is ignored).
+ * The scores are fp32 sums of exact products: on the fp32 pipes, or -- bf16 rows, at least 32 tokens per SM, at most
+ * 32 queries -- as bf16 tensor-core products of the update with a three-term bf16 split of each fp32 query, summed in fp32.
  * Replaces DattnStack.write / _WriteDelta.forward and the kernel _write_stk_kernel (fused_dattn.py:561-585,
  * :663-691) and, when R is requested without Q, the scale kernel used by DattnStack.rstd (fused_dattn.py:698-708). */
 int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, float *DOTS, int64_t n_tok, int d, int N,
