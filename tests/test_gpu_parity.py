@@ -498,7 +498,8 @@ def test_error_behaviour(FD):
 # ------------------------------------------------------------------------------------------------------------
 def test_full_size_properties(FD):
     """At configuration 2's size the oracle is too slow, so the checks are properties: (a) per-token independence --
-    the chain on the first 4096 tokens alone reproduces the slice of the full chain bit for bit; (b) the tracked
+    the chain on the first 8192 tokens alone (still a batch the tensor-core write takes, with other tile sizes in all
+    three kernels) reproduces the slice of the full chain bit for bit; (b) the tracked
     coefficients of every token sum to the read's mass; (c) zero queries reduce the chain to the decay-only closed
     form h0 + sum_i lambda^(R - floor(i/K)) D_i (within the bf16 state rounding), and tc == c0 bitwise."""
     d, K, R, b, t = 1024, 4, 6, 8, 4096
@@ -532,9 +533,9 @@ def test_full_size_properties(FD):
         return x.detach(), coeffs.detach(), prior.detach(), (h0r.grad, cell.query.grad) if grad else None
 
     x_full, tc_full, c0, grads_full = run(h0, D, Q, True)
-    x_part, tc_part, _, grads_part = run(h0[:1], D[:, :1], Q, True)
-    assert torch.equal(x_full[:1], x_part) and torch.equal(tc_full[:1], tc_part)
-    assert torch.equal(grads_full[0][:1], grads_part[0])
+    x_part, tc_part, _, grads_part = run(h0[:2], D[:, :2], Q, True)
+    assert torch.equal(x_full[:2], x_part) and torch.equal(tc_full[:2], tc_part)
+    assert torch.equal(grads_full[0][:2], grads_part[0])
     assert torch.isfinite(grads_full[1]).all() and torch.isfinite(grads_full[0]).all()
     assert float((tc_full.sum(-1) - c0.sum()).abs().max()) < 1e-4 * float(c0.sum())
     x_zero, tc_zero, c0z, _ = run(h0, D, torch.zeros_like(Q), False)
