@@ -322,6 +322,45 @@ def main():
                 ms_per_step, launch_mode, clocks = graph_ms, "CUDA graph replay of the whole pass", clocks_g
     value = world * n_tok / (ms_per_step * 1e-3)
 
+    # ---- the harness's own share of a pass: the N block stand-ins h = x + D_s, timed alone (reported, not subtracted)
+    hx, hd = P.h0.detach(), P.D[0]
+    for _ in range(3):
+        _ = hx + hd
+
+    def harness_adds():
+        for _ in range(N):
+            _ = hx + hd
+    harness_ms = timed(harness_adds, 5) / 5
+
+    # ---- decode-style depth sweep (the forward-only workload): the same pass at R = 2, 4, 8 as a graph replay
+    depth_sweep = None
+    if not w["backward"] and world == 1 and not args.no_graph:
+        depth_sweep = []
+        for r_iter in (2, 4, 8, w["R"]):
+            wr = dict(w, R=r_iter)
+            Pr = Pass(wr, dev, seed=rank)
+            Pr.cell.fuse_prologue = P.cell.fuse_prologue
+            for _ in range(3):
+                Pr.run()
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                Pr.run()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                Pr.run()
+            for _ in range(3):
+                gr.replay()
+            ms_r = timed(gr.replay, 20) / 20
+            n_r = wr["K"] * r_iter
+            units = algorithmic_units(n_r, False)
+            depth_sweep.append({"R": r_iter, "updates": n_r, "ms_per_pass": ms_r,
+                                "us_per_step": ms_r * 1e3 / n_r,        # one write + one read (+ the harness add)
+                                "algorithmic_gbs": units * n_tok * d * elem / (ms_r * 1e-3) / 1e9})
+            assert FD.device_error() == 0
+
     # ---- roofline of the dominant kernel: algorithmic bytes of its launches over their event time -------------
     peak, peak_kind = measured_peak()
     per_kind = {}
@@ -485,7 +524,11 @@ def main():
                                                      f"{N * n_tok * d * elem / 2**20:.0f} MiB per GPU)",
                        "parallelism": f"tokens x{world}" if world > 1 else "single GPU",
                        "launch": launch_mode, "eager_ms_per_step": eager_ms_per_step,
-                       "pass_algorithmic_gbs": pass_gbs, "pass_frac_of_peak": pass_gbs / peak, "kernels": kernels},
+                       "pass_algorithmic_gbs": pass_gbs, "pass_frac_of_peak": pass_gbs / peak,
+                       "harness_adds_ms_per_step": harness_ms,
+                       "pass_frac_of_peak_without_harness_adds":
+                           pass_units * n_tok * d * elem / ((ms_per_step - harness_ms) * 1e-3) / 1e9 / peak,
+                       "depth_sweep": depth_sweep, "kernels": kernels},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
             "clocks": clocks.summary(),
         }
