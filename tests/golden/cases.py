@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-# BASELINE configuration 1: fp32, B=2, T=256, d=768, K=4, R=4, lambda=0.25, eps=1e-6, seed 0
+# benchmark configuration 1: fp32, B=2, T=256, d=768, K=4, R=4, lambda=0.25, eps=1e-6, seed 0
 CFG1 = dict(b=2, t=256, d=768, K=4, R=4, beta=0.75, eps=1e-6, sigma_h0=1.0, sigma_d=0.5, sigma_q=0.02, seed=0)
 # tokens of configuration 1 whose full read states are stored in the fixture
 CFG1_TOKENS = (0, 1, 2, 3, 100, 255, 256, 257, 300, 383, 384, 450, 509, 510, 511, 77)

@@ -20,7 +20,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 import cases  # noqa: E402
 
-REF = os.environ.get("LOOPBACK_REF", "/root/reference")
+REF = os.environ.get("LOOPBACK_REF")
+if not REF or not os.path.isfile(os.path.join(REF, "looped_transformer.py")):
+    raise SystemExit("set LOOPBACK_REF to a checkout of the reference (the directory holding looped_transformer.py)")
 sys.path.insert(0, REF)
 os.environ["LOOP_DATTN_FUSED"] = "0"
 import looped_transformer as M  # noqa: E402  (the reference)

@@ -355,7 +355,7 @@ def test_golden_chains(FD, case, path):
 
 
 def test_config1_full_size(FD):
-    """BASELINE configuration 1 (fp32, 512 tokens, d=768, K=4, R=4, seed 0): every read state against the
+    """benchmark configuration 1 (fp32, 512 tokens, d=768, K=4, R=4, seed 0): every read state against the
     reference's, at the stored tokens and through per-token sums of every state."""
     CFG1 = np.load(os.path.join(G, "cfg1_chain_fp32.npz"))
     c = cases.CFG1
@@ -494,7 +494,7 @@ def test_error_behaviour(FD):
 
 
 # ------------------------------------------------------------------------------------------------------------
-# 6. full-size properties (BASELINE configuration 2 shapes: 32768 tokens, d=1024, bf16, N=24)
+# 6. full-size properties (benchmark configuration 2 shapes: 32768 tokens, d=1024, bf16, N=24)
 # ------------------------------------------------------------------------------------------------------------
 def test_full_size_properties(FD):
     """At configuration 2's size the oracle is too slow, so the checks are properties: (a) per-token independence --

@@ -143,7 +143,7 @@ def test_clamped_prior_case_is_exercised():
 
 
 def test_config1_chain_fp32():
-    """BASELINE configuration 1 at full size through the C oracle (fp32) and the torch restatement."""
+    """benchmark configuration 1 at full size through the C oracle (fp32) and the torch restatement."""
     c = cases.CFG1
     h0, D, Q, Gu = cases.chain_inputs(**c)
     assert cases.checksum(h0, D, Q, Gu) == pytest.approx(float(CFG1["checksum"]), rel=1e-12)
