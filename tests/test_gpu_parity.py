@@ -42,6 +42,13 @@ def L():
     return lib
 
 
+@pytest.fixture(autouse=True)
+def _default_kernel_choice(L):
+    """A test that forces a kernel through lb_set_option leaves the choice by size behind, pass or fail."""
+    yield
+    L.set_option("write_tt", 0)
+
+
 def cuda(x):
     return x.cuda() if torch.is_tensor(x) else x
 
@@ -375,12 +382,15 @@ def test_config1_full_size(FD):
 # ------------------------------------------------------------------------------------------------------------
 # 4. chains against the oracle at sizes the fixtures do not hold; teacher-forced bf16 protocol
 # ------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("d,K,R,n_tok", [(1024, 4, 6, 96), (1536, 6, 4, 40), (3072, 8, 3, 24), (2048, 5, 4, 64)])
-def test_bf16_chain_teacher_forced(FD, d, K, R, n_tok):
+@pytest.mark.parametrize("write_kernel", [0, 3])      # by size / the tensor-core write where it applies
+@pytest.mark.parametrize("d,K,R,n_tok", [(1024, 4, 6, 96), (1536, 6, 4, 40), (3072, 8, 3, 24), (2048, 5, 4, 64),
+                                         (2048, 5, 16, 64)])
+def test_bf16_chain_teacher_forced(FD, L, d, K, R, n_tok, write_kernel):
     """Each read of a bf16 chain, given the GPU chain's own stored updates, base and installed coefficients,
     against the C oracle's fp32 evaluation of exactly those inputs: <= 2e-2 * RMS(out) max-abs per read."""
     from loopback_b200.cell import LoopDeltaAttnRes
     N = K * R
+    L.set_option("write_tt", write_kernel)
     h0, D, Q, Gu = cases.chain_inputs(1, n_tok, d, K, R, seed=d + K, dtype=torch.bfloat16, sigma_d=0.3)
     cell = LoopDeltaAttnRes(d, R, K, beta=0.75, eps=1e-6).cuda()
     with torch.no_grad():
@@ -408,6 +418,7 @@ def test_bf16_chain_teacher_forced(FD, d, K, R, n_tok):
                 assert err <= 2e-2 * rms, (s, err, rms)
                 assert rel(coeffs.reshape(n_tok, s + 1), tc) < 1e-4
             x = x_new
+    L.set_option("write_tt", 0)
     print(f"d={d} N={N}: worst per-read error {worst:.3e} RMS")
 
 
