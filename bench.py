@@ -54,36 +54,49 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 100 ms from before the warm-up to the end of
+    the run; `window()` brackets a timed region and `summary(window)` reports the samples that fell inside it."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.rows, self.proc, self.index = [], None, index
-
-    def __enter__(self):
+        if index is None:
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:  # noqa: BLE001
             self.proc = None
-        return self
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
-    def __exit__(self, *a):
+    def stop(self):
         if self.proc is not None:
             self.proc.terminate()
-        return False
+            self.proc = None
 
-    def summary(self):
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+    class _Window:
+        def __enter__(self):
+            self.t0 = time.monotonic()
+            return self
+
+        def __exit__(self, *a):
+            self.t1 = time.monotonic()
+            return False
+
+    def window(self):
+        return ClockSampler._Window()
+
+    def summary(self, win):
+        rows = [r for (ts, r) in self.rows if win.t0 <= ts <= win.t1 + 0.1 and len(r) >= 6]
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [nm for k, nm in enumerate(names) if any(len(r) >= 6 and r[2 + k].lower() == "active" for r in self.rows)]
+        reasons = [nm for k, nm in enumerate(names) if any(r[2 + k].lower() == "active" for r in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -260,6 +273,7 @@ def main():
         return float(ms.item())
 
     # ---- device-resident timing, with per-launch events on the dominant kernels -------------------------------
+    sampler = ClockSampler(local if rank == 0 else None)       # rank 0 reports its own GPU's clocks
     for _ in range(args.warmup):
         one_pass()
     launches = []
@@ -278,7 +292,7 @@ def main():
 
     FD.LAUNCH_TIMER = Timer
     count0 = L.LAUNCHES["count"]
-    with ClockSampler(local) as clocks:
+    with sampler.window() as clocks:
         total_ms = timed(one_pass, args.steps)
     gpu_launches = (L.LAUNCHES["count"] - count0) // args.steps
     FD.LAUNCH_TIMER = None
@@ -315,7 +329,7 @@ def main():
             for _ in range(3):
                 graph_pass()
             assert FD.device_error() == 0
-            with ClockSampler(local) as clocks_g:
+            with sampler.window() as clocks_g:
                 graph_ms = timed(graph_pass, args.steps) / args.steps
             assert FD.device_error() == 0, "a kernel gave up a bounded wait"
             if graph_ms < ms_per_step:
@@ -530,9 +544,10 @@ def main():
                            pass_units * n_tok * d * elem / ((ms_per_step - harness_ms) * 1e-3) / 1e9 / peak,
                        "depth_sweep": depth_sweep, "kernels": kernels},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
-            "clocks": clocks.summary(),
+            "clocks": sampler.summary(clocks),
         }
         print(json.dumps(line), flush=True)
+    sampler.stop()
     if world > 1:
         dist.destroy_process_group()
 
