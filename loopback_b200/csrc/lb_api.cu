@@ -377,11 +377,12 @@ static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int q
         while (fr > 1 && tok_tiles * ((nch + fr - 1) / fr) < di.sms) --fr;
         cg = (nch + fr - 1) / fr;
     }
-    // ring depth: 8 stages of a full-size (16 KiB) tile; small tiles (decode-sized batches) get a deeper ring so that
-    // a CTA still keeps ~128 KiB in flight
+    // ring depth: 6 stages of a full-size (12-16 KiB) tile measured best (8 and more cost 2-4 %: more requests in
+    // flight than the memory system orders well); small tiles (decode-sized batches) get a deeper ring so that a CTA
+    // still keeps ~128 KiB in flight
     const int stage_bytes = fr * ncw * lb::kChunkBytes;
-    int stages = g_opt.fwd_stages > 0 ? g_opt.fwd_stages : 8;
-    if (g_opt.fwd_stages <= 0 && stage_bytes * stages < 128 * 1024) stages = 128 * 1024 / stage_bytes;
+    int stages = g_opt.fwd_stages > 0 ? g_opt.fwd_stages : 6;
+    if (g_opt.fwd_stages <= 0 && stage_bytes < 12 * 1024) stages = 128 * 1024 / stage_bytes;
     if (stages > 32) stages = 32;
     while (stages > 2 && lb::read_fwd_smem_bytes(fr, ncw, stages) > kMaxSmem) --stages;
 
