@@ -37,7 +37,7 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 struct Options {
     int fwd_stages = 0, bwd_stages = 0, fwd_fr = 0, grid_cap = 0, fwd_warps = 0, bwd_warps = 0, bwd_wpt = 0,
-        tma_per_chunk = 0, write_tt = 0, write_mt = 0;
+        tma_per_chunk = 0, write_tt = 0, write_mt = 0, fwd_sps = 0;
 } g_opt;
 
 struct DeviceInfo {
@@ -92,7 +92,7 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 //                    box = 512 bytes x box_chunks chunks x box_tok tokens: a whole tile in one copy, token-major.
 //                    Needs d to be a multiple of the chunk width.
 int make_map(CUtensorMap *m, const void *base, int dtype, long long n_tok, int d, int outer, int box_tok,
-             int box_chunks) {
+             int box_chunks, int box_outer = 1) {
     auto fn = encode_fn();
     if (!fn) return fail(LB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
@@ -116,7 +116,7 @@ int make_map(CUtensorMap *m, const void *base, int dtype, long long n_tok, int d
     if (outer > 0) {
         dims[rank] = (cuuint64_t)outer;
         strides[rank - 1] = (cuuint64_t)d * elem * (cuuint64_t)n_tok;
-        box[rank] = 1;
+        box[rank] = (cuuint32_t)box_outer;
         ++rank;
     }
     CUresult r = fn(m, dtype == LB_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
@@ -197,6 +197,7 @@ int lb_set_option(const char *name, int value) {
     else if (!strcmp(name, "tma_per_chunk")) g_opt.tma_per_chunk = value;
     else if (!strcmp(name, "write_tt")) g_opt.write_tt = value;
     else if (!strcmp(name, "write_mt")) g_opt.write_mt = value;
+    else if (!strcmp(name, "fwd_sps")) g_opt.fwd_sps = value;
     else return fail(LB_ERR_ARG, "unknown option '%s'", name);
     return LB_OK;
 }
@@ -380,14 +381,20 @@ static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int q
     // ring depth: 6 stages of a full-size (12-16 KiB) tile measured best (8 and more cost 2-4 %: more requests in
     // flight than the memory system orders well); small tiles (decode-sized batches) get a deeper ring so that a CTA
     // still keeps ~128 KiB in flight
-    const int stage_bytes = fr * ncw * lb::kChunkBytes;
+    // Small tiles also take several sources per stage (one TMA box over the source axis): the hand-shake of a stage
+    // costs about as much for 4 KiB as for 16 KiB, and a decode-sized read is made of nothing else.
+    const int tile_bytes = fr * ncw * lb::kChunkBytes;
+    int sps = 1;
+    if (rank4 && n >= 4) sps = tile_bytes <= 4 * 1024 ? 4 : (tile_bytes <= 8 * 1024 ? 2 : 1);
+    if (rank4 && g_opt.fwd_sps >= 1 && g_opt.fwd_sps <= 4) sps = g_opt.fwd_sps;
+    const int stage_bytes = sps * tile_bytes;
     int stages = g_opt.fwd_stages > 0 ? g_opt.fwd_stages : 6;
     if (g_opt.fwd_stages <= 0 && stage_bytes < 12 * 1024) stages = 128 * 1024 / stage_bytes;
     if (stages > 32) stages = 32;
-    while (stages > 2 && lb::read_fwd_smem_bytes(fr, ncw, stages) > kMaxSmem) --stages;
+    while (stages > 2 && lb::read_fwd_smem_bytes(fr, ncw, stages, sps) > kMaxSmem) --stages;
 
     CUtensorMap tmV, tmB, tmH;
-    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, bt, rank4 ? fr * wpt : 0))) return rc;
+    if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, bt, rank4 ? fr * wpt : 0, sps))) return rc;
     if ((rc = make_map(&tmB, base, dtype, n_tok, d, 0, bt, rank4 ? fr * wpt : 0))) return rc;
     if ((rc = make_map(&tmH, h0 ? h0 : base, dtype, n_tok, d, 0, bt, rank4 ? fr * wpt : 0))) return rc;
 
@@ -397,7 +404,7 @@ static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int q
     p.cbar = cbar; p.tc_prev = tc_prev; p.lam = lam; p.blend = h0 ? 1 : 0; p.beta = beta;
     p.c0 = c0; p.out = out; p.TC = TC; p.LG = LG; p.LSE = LSE; p.LSE0 = LSE0;
     p.n_tok = n_tok; p.d = d; p.n = n; p.chunks = nch; p.wpt = wpt; p.col_groups = cg; p.tok_tiles = tok_tiles;
-    p.stages = stages;
+    p.stages = stages; p.sps = sps;
     p.rank4 = rank4 ? 1 : 0;
     p.inv_sqrt_d = 1.0f / sqrtf((float)d);
     p.err_word = di.err_word;

@@ -34,11 +34,12 @@ struct ReadFwdParams {
     long long tok_tiles;   // ceil(n_tok / tokens per tile)
     int rank4;             // 1: one 4-D TMA box per stage (d a multiple of the chunk width), 0: one box per chunk
     int stages;
+    int sps;               // sources per stage (1..4; > 1 only with rank4)
     float inv_sqrt_d;
     int *err_word;         // device error word (see lb_device_error)
 };
 
-size_t read_fwd_smem_bytes(int fr, int ncw, int stages);
+size_t read_fwd_smem_bytes(int fr, int ncw, int stages, int sps);
 cudaError_t launch_read_fwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmBase,
                             const CUtensorMap &tmH0, const ReadFwdParams &p, int grid, cudaStream_t stream);
 cudaError_t launch_scores(int dtype, const void *V, const float *q, float *dots, long long n_tok, int d, int n,

@@ -38,8 +38,8 @@ struct FwdSmemTail {
     uint64_t sempty[2];
 };
 
-size_t read_fwd_smem_bytes(int fr, int ncw, int stages) {
-    return 1024 + (size_t)stages * (size_t)fr * ncw * kChunkBytes + sizeof(FwdSmemTail);
+size_t read_fwd_smem_bytes(int fr, int ncw, int stages, int sps) {
+    return 1024 + (size_t)stages * (size_t)sps * (size_t)fr * ncw * kChunkBytes + sizeof(FwdSmemTail);
 }
 
 template <typename T, int FR, int NCW>
@@ -58,7 +58,11 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     // shared-window addresses of the regions of the dynamic shared memory
     extern __shared__ uint8_t smem_raw[];
     const uint32_t stages_a = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t tail_a = stages_a + (uint32_t)p.stages * kStageBytes;
+    // a stage holds the tile of SPS consecutive sources (one TMA box): small tiles pay the per-stage hand-shake once
+    // for up to 4 sources; the base tile takes a stage of its own and uses its first kStageBytes
+    const int SPS = p.sps;
+    const uint32_t kPitch = (uint32_t)SPS * kStageBytes;
+    const uint32_t tail_a = stages_a + (uint32_t)p.stages * kPitch;
     const uint32_t wtab_a = tail_a + offsetof(FwdSmemTail, wtab);
     const uint32_t c0_a = tail_a + offsetof(FwdSmemTail, c0), lc_a = tail_a + offsetof(FwdSmemTail, lc);
     const uint32_t mass_a = tail_a + offsetof(FwdSmemTail, mass), abort_a = tail_a + offsetof(FwdSmemTail, abort_flag);
@@ -113,7 +117,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             float2 acc[FR][P];
             {   // item 0: the base tile
                 if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+                const uint32_t sb = stages_a + (uint32_t)st * kPitch;
 #pragma unroll
                 for (int k = 0; k < FR; ++k) S::unpack2(lds_v4(sb + foff[k]), acc[k]);
                 __syncwarp();
@@ -125,7 +129,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 // storage type's rounding after each operation, i.e. what the caller's own tensor arithmetic gives
                 // (looped_transformer.py:381)
                 if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+                const uint32_t sb = stages_a + (uint32_t)st * kPitch;
                 const float beta = p.beta;
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
@@ -145,23 +149,45 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             }
             if (alive && !mbar_wait(sfull_a + 8u * buf, (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
             uint32_t wa = wtab_a + buf * kWtabBytes + 4u * t;
-            for (int i = 0; i < n; ++i, wa += 4u * BT) {
-                if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
-                const float wi = lds_f32(wa);
-                const float2 w2 = make_float2(wi, wi);
-                uint4 u[FR];
+            if (SPS == 1) {
+                for (int i = 0; i < n; ++i, wa += 4u * BT) {
+                    if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                    const uint32_t sb = stages_a + (uint32_t)st * kPitch;
+                    const float wi = lds_f32(wa);
+                    const float2 w2 = make_float2(wi, wi);
+                    uint4 u[FR];
 #pragma unroll
-                for (int k = 0; k < FR; ++k) u[k] = lds_v4(sb + foff[k]);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty_a + 8u * st);
-                if (++st == NS) { st = 0; ph ^= 1u; }
+                    for (int k = 0; k < FR; ++k) u[k] = lds_v4(sb + foff[k]);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                    if (++st == NS) { st = 0; ph ^= 1u; }
 #pragma unroll
-                for (int k = 0; k < FR; ++k) {
-                    float2 v[P];
-                    S::unpack2(u[k], v);
+                    for (int k = 0; k < FR; ++k) {
+                        float2 v[P];
+                        S::unpack2(u[k], v);
 #pragma unroll
-                    for (int e = 0; e < P; ++e) acc[k][e] = __ffma2_rn(w2, v[e], acc[k][e]);
+                        for (int e = 0; e < P; ++e) acc[k][e] = __ffma2_rn(w2, v[e], acc[k][e]);
+                    }
+                }
+            } else {
+                for (int i = 0; i < n; i += SPS) {
+                    if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                    uint32_t sb = stages_a + (uint32_t)st * kPitch;
+                    const int m = min(SPS, n - i);               // sources past n in the box are never read
+                    for (int j = 0; j < m; ++j, wa += 4u * BT, sb += kStageBytes) {
+                        const float wi = lds_f32(wa);
+                        const float2 w2 = make_float2(wi, wi);
+#pragma unroll
+                        for (int k = 0; k < FR; ++k) {
+                            float2 v[P];
+                            S::unpack2(lds_v4(sb + foff[k]), v);
+#pragma unroll
+                            for (int e = 0; e < P; ++e) acc[k][e] = __ffma2_rn(w2, v[e], acc[k][e]);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                    if (++st == NS) { st = 0; ph ^= 1u; }
                 }
             }
             __syncwarp();
@@ -193,14 +219,15 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 const int tok0 = (int)(tt * BT);
                 const int chunk0 = cg * CPT;
                 const int nch = min(CPT, p.chunks - chunk0);
-                for (int item = first_item; item < n; ++item) {
+                for (int item = first_item; item < n; item += (item < 0 ? 1 : SPS)) {
                     if (!mbar_wait(empty_a + 8u * st, ph ^ 1u, wc, kDevWaitEmpty)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t sb = stages_a + (uint32_t)st * kStageBytes, fb = full_a + 8u * st;
-                    if (p.rank4) {          // one box: CPT chunks x BT tokens (chunks past the row are zero-filled)
-                        mbar_arrive_expect_tx(fb, kStageBytes);
+                    const uint32_t sb = stages_a + (uint32_t)st * kPitch, fb = full_a + 8u * st;
+                    if (p.rank4) {          // one box: CPT chunks x BT tokens (x SPS sources); what lies past the row or
+                                            // the stack is zero-filled and counts toward the bytes all the same
+                        mbar_arrive_expect_tx(fb, item < 0 ? kStageBytes : kPitch);
                         if (item < 0) tma_load_3d(sb, (item == first_item) ? &tmBase : &tmH0, fb, 0, chunk0, tok0);
                         else tma_load_4d(sb, &tmV, fb, 0, chunk0, tok0, item);
                     } else {
@@ -325,7 +352,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 template <typename T, int FR, int NCW>
 static cudaError_t launch_fwd(const CUtensorMap &tmV, const CUtensorMap &tmBase, const CUtensorMap &tmH0,
                               const ReadFwdParams &p, int grid, cudaStream_t stream) {
-    size_t smem = read_fwd_smem_bytes(FR, NCW, p.stages);
+    size_t smem = read_fwd_smem_bytes(FR, NCW, p.stages, p.sps);
     cudaError_t e = cudaFuncSetAttribute(read_fwd_kernel<T, FR, NCW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     read_fwd_kernel<T, FR, NCW><<<grid, (NCW + 1 + kFwdScalarWarps) * 32, smem, stream>>>(tmV, tmBase, tmH0, p);
