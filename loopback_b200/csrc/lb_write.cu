@@ -287,8 +287,9 @@ cudaError_t launch_write(int dtype, const WriteParams &p, int sms, cudaStream_t 
     const int row_frags = p.d / (dtype == LB_DTYPE_BF16 ? 8 : 4);
     if (p.write_tt == 0 && p.n_tok <= 4LL * sms && row_frags <= kWrSmallThreads * kWrSmallFrags) {
         // a decode-sized batch: tiles of 32 tokens would leave most SMs idle
-        int qsplit = (int)(sms / p.n_tok), qgroups = (p.nq + 31) / 32;
-        if (qsplit > qgroups) qsplit = qgroups;
+        // one CTA per (token, group of 32 queries) while that stays within a few waves of small CTAs
+        int qgroups = (p.nq + 31) / 32, qsplit = qgroups;
+        while (qsplit > 1 && p.n_tok * qsplit > 4LL * sms) --qsplit;
         if (qsplit < 1) qsplit = 1;
         const dim3 grid((unsigned)p.n_tok, (unsigned)qsplit);
         if (dtype == LB_DTYPE_BF16) write_small_kernel<__nv_bfloat16><<<grid, kWrSmallThreads, 0, stream>>>(p);
