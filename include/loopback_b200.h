@@ -60,7 +60,8 @@ int lb_device_error(int clear);
  * "fwd_warps", "bwd_warps" (consumer warps per CTA: 8, 12 or 16), "bwd_wpt" (warps per token), "grid_cap" (CTAs),
  * "tma_per_chunk" (one 3-D box per chunk instead of one 4-D box per stage), "write_tt" (1 or 2: tokens per lane of the
  * tiled write kernel, whatever the batch size; 3: the tensor-core write kernel whatever the batch size),
- * "write_mt" (16-token tiles per consumer warp of the tensor-core write kernel: 1 or 2). Value 0 restores the default
+ * "write_mt" (16-token tiles per consumer warp of the tensor-core write kernel: 1 or 2),
+ * "fwd_sps" (sources per TMA stage of the forward read: 1, 2 or 4). Value 0 restores the default
  * (chosen by size). Returns LB_ERR_ARG for an unknown name. */
 int lb_set_option(const char *name, int value);
 

@@ -47,6 +47,7 @@ def _default_kernel_choice(L):
     """A test that forces a kernel through lb_set_option leaves the choice by size behind, pass or fail."""
     yield
     L.set_option("write_tt", 0)
+    L.set_option("fwd_sps", 0)
 
 
 def cuda(x):
@@ -239,6 +240,21 @@ def test_read_bf16_against_fp64(FD, b, t, d, n):
             continue
         e_got, e_ref = rel(got[k], want[k]), rel(ref_bf16[k], want[k])
         assert e_got <= 2.0 * e_ref + 2e-3, (k, e_got, e_ref)
+
+
+@pytest.mark.parametrize("b,t,d,n,dtype", [(1, 64, 2048, 11, torch.bfloat16), (2, 100, 1024, 7, torch.float32),
+                                           (1, 24, 512, 21, torch.bfloat16)])
+def test_sources_per_stage_do_not_change_a_bit(FD, L, b, t, d, n, dtype):
+    """Small tiles take 1, 2 or 4 sources per TMA stage; the order of the arithmetic does not depend on it."""
+    ins = cases.read_inputs(b, t, d, n, dtype, seed=7 * n + d)
+    got = []
+    for sps in (1, 2, 4):
+        L.set_option("fwd_sps", sps)
+        got.append(run_read_gpu(FD, *ins, False))
+    L.set_option("fwd_sps", 0)
+    for other in got[1:]:
+        for key in ("out", "tc", "dd", "dq"):
+            assert torch.equal(got[0][key], other[key]), key
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
