@@ -62,7 +62,9 @@ int lb_device_error(int clear);
  * tiled write kernel, whatever the batch size; 3: the tensor-core write kernel whatever the batch size),
  * "write_mt" (16-token tiles per consumer warp of the tensor-core write kernel: 1 or 2),
  * "fwd_sps" (sources per TMA stage of the forward read: 1, 2 or 4). Value 0 restores the default
- * (chosen by size). Returns LB_ERR_ARG for an unknown name. */
+ * (chosen by size); the name "reset_all" restores every knob. Returns LB_ERR_ARG for an unknown name.
+ * The knobs are one process-wide table without a lock: set them from one thread, while no other thread is inside
+ * a call of this library. */
 int lb_set_option(const char *name, int value);
 
 /* Update write: V[s] = round(h - x); R[s] = key scale of the rounded update; if Q != NULL also the cached scores

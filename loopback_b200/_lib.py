@@ -102,3 +102,8 @@ def device_error(clear: bool = True) -> int:
 
 def set_option(name: str, value: int) -> None:
     check(lib().lb_set_option(name.encode(), int(value)), f"set_option({name})")
+
+
+def reset_options() -> None:
+    """Every tuning knob back to its default (the choice by size)."""
+    check(lib().lb_set_option(b"reset_all", 0), "set_option(reset_all)")

@@ -187,7 +187,8 @@ int lb_device_error(int clear) {
 
 int lb_set_option(const char *name, int value) {
     if (!name) return fail(LB_ERR_ARG, "option name is NULL");
-    if (!strcmp(name, "fwd_stages")) g_opt.fwd_stages = value;
+    if (!strcmp(name, "reset_all")) g_opt = Options();
+    else if (!strcmp(name, "fwd_stages")) g_opt.fwd_stages = value;
     else if (!strcmp(name, "bwd_stages")) g_opt.bwd_stages = value;
     else if (!strcmp(name, "fwd_fr")) g_opt.fwd_fr = value;
     else if (!strcmp(name, "grid_cap")) g_opt.grid_cap = value;
@@ -208,7 +209,8 @@ int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, fl
     if (rc) return rc;
     if (!h || !x || !V) return fail(LB_ERR_ARG, "lb_write: h, x and V must be non-NULL");
     if (N <= 0 || s < 0 || s >= N) return fail(LB_ERR_ARG, "lb_write: step %d outside [0, %d)", s, N);
-    if (Q && (!DOTS || !R || NQ < 0 || NQ > N)) return fail(LB_ERR_ARG, "lb_write: scores need R, DOTS and 0 <= NQ <= N");
+    if (!R) Q = nullptr;                       // without R only V[s] is written: Q is ignored
+    if (Q && (!DOTS || NQ < 0 || NQ > N)) return fail(LB_ERR_ARG, "lb_write: scores need DOTS and 0 <= NQ <= N");
     if (!aligned16(h) || !aligned16(x) || !aligned16(V) || (Q && !aligned16(Q)))
         return fail(LB_ERR_ALIGN, "lb_write: h, x, V and Q must be 16-byte aligned");
     DeviceInfo di;

@@ -46,8 +46,7 @@ def L():
 def _default_kernel_choice(L):
     """A test that forces a kernel through lb_set_option leaves the choice by size behind, pass or fail."""
     yield
-    L.set_option("write_tt", 0)
-    L.set_option("fwd_sps", 0)
+    L.reset_options()
 
 
 def cuda(x):
@@ -313,26 +312,61 @@ def test_golden_single_reads(FD, case):
             assert e_got <= 2.0 * e_ref + 2e-3, (k, e_got, e_ref)
 
 
-def chain_gpu(FD, h0, D, Q, Gu, K, R, beta, eps, scores, with_grad, list_layout=False):
+def reference_combine(cell, FD, proposal, h0, deltas, coeffs, prior_coeffs, loop_idx, block_idx, keys=None, stack=None):
+    """The stacked branch of the reference trainer cell's `combine`, restated on the test side
+    (modeling_looped_transformer.py:148-169): the prologue in torch, then the exact call the trainer makes,
+    FusedDattnReadStk.apply(stack, step, q, base, base_coeffs, next_prior, *deltas, *R_list)."""
+    step = loop_idx * cell.num_blocks + block_idx
+    at_boundary = block_idx == cell.num_blocks - 1
+    base = proposal + cell.beta * (h0 - proposal) if at_boundary else proposal
+    b, t, _ = proposal.shape
+    one_tok = torch.ones(b, t, 1, device=proposal.device, dtype=torch.float32)
+    one_prior = torch.ones(1, device=proposal.device, dtype=torch.float32)
+    base_coeffs = one_tok if coeffs is None else torch.cat((coeffs, one_tok), dim=-1)
+    next_prior = one_prior if prior_coeffs is None else torch.cat((prior_coeffs, one_prior), dim=-1)
+    if at_boundary:
+        r = 1.0 - cell.beta
+        base_coeffs, next_prior = r * base_coeffs, r * next_prior
+    if keys is not None and len(keys) < len(deltas):
+        keys.append(stack.rstd(step, deltas[-1], cell.eps))
+    if len(deltas) == 1:
+        return base, base_coeffs, next_prior
+    R_list = keys if keys is not None else [FD._alias(stack.R, i) for i in range(len(deltas))]
+    out, target = FD.FusedDattnReadStk.apply(stack, step, cell.query[step - 1], base, base_coeffs, next_prior,
+                                             *deltas, *R_list)
+    return out, target, next_prior
+
+
+# how the chain calls the read: the cell's fast path (prologue inside the kernels, one node per step), the cell with
+# its prologue in torch (FusedDattnReadStk, the entry point the reference trainer calls), the reference's own combine
+# restated above
+COMBINE_PATHS = ["fused", "dropin", "reference_combine"]
+
+
+def chain_gpu(FD, h0, D, Q, Gu, K, R, beta, eps, scores, with_grad, list_layout=False, path="fused", use_keys=True):
     """The cell driven as the model drives it (blocks x -> x + D_s), on the GPU, through the drop-in module."""
     from loopback_b200.cell import LoopDeltaAttnRes
     N = K * R
     b, t, d = h0.shape
     cell = LoopDeltaAttnRes(d, R, K, beta=beta, eps=eps).cuda()
+    cell.fuse_prologue = path == "fused"
     with torch.no_grad():
         if N > 1:
             cell.query.copy_(Q[:N - 1].cuda())
     h0g = h0.detach().clone().cuda().requires_grad_(with_grad)
     Dg = D.detach().clone().cuda().requires_grad_(with_grad)
     stack = None if list_layout else cell.new_stack((b, t, d), h0.dtype, "cuda", scores=scores)
-    x, deltas, keys, coeffs, prior, states = h0g, [], [], None, None, []
+    x, deltas, keys, coeffs, prior, states = h0g, [], ([] if use_keys else None), None, None, []
     with torch.set_grad_enabled(with_grad):
         loss = 0.0
         for s in range(N):
             l, blk = divmod(s, K)
             hs = x + Dg[s]
             deltas.append(stack.write(s, hs, x) if stack is not None else hs - x)
-            x, coeffs, prior = cell.combine(hs, h0g, deltas, coeffs, prior, l, blk, keys=keys, stack=stack)
+            if path == "reference_combine" and stack is not None:
+                x, coeffs, prior = reference_combine(cell, FD, hs, h0g, deltas, coeffs, prior, l, blk, keys=keys, stack=stack)
+            else:
+                x, coeffs, prior = cell.combine(hs, h0g, deltas, coeffs, prior, l, blk, keys=keys, stack=stack)
             states.append(x)
             if with_grad:
                 loss = loss + (x.float() * Gu[s].cuda()).sum()
@@ -346,7 +380,8 @@ def chain_gpu(FD, h0, D, Q, Gu, K, R, beta, eps, scores, with_grad, list_layout=
 
 @pytest.mark.parametrize("case", cases.CHAIN_CASES, ids=[c[0] for c in cases.CHAIN_CASES])
 @pytest.mark.parametrize("path", ["scores", "stack", "list"])
-def test_golden_chains(FD, case, path):
+@pytest.mark.parametrize("combine", COMBINE_PATHS)
+def test_golden_chains(FD, case, path, combine):
     """K x R chains against the reference's states, tracked coefficients and gradients; `scores` is the stacked
     layout with cached scores (the trainer's default), `stack` the stacked layout without, `list` one tensor per
     update (tests/test_dattn_stack.py:96-118)."""
@@ -355,8 +390,10 @@ def test_golden_chains(FD, case, path):
     h0, D, Q, Gu = cases.chain_inputs(b, t, d, K, R, seed, dtype=DT[dtn], sigma_q=0.3)
     assert cases.checksum(h0, D, Q, Gu) == pytest.approx(float(CH[f"{name}/checksum"]), rel=1e-12)
     N = K * R
+    if path == "list" and combine != "fused":
+        pytest.skip("the list layout has one combine path")
     got = chain_gpu(FD, h0, D, Q, Gu, K, R, 0.75, 1e-6, scores=path == "scores", with_grad=with_grad,
-                    list_layout=path == "list")
+                    list_layout=path == "list", path=combine)
     assert torch.equal(got["c0_last"].cpu(), torch.from_numpy(CH[f"{name}/ref/c0_last"]))
     if dtn == "float32":
         assert rel(got["states"], CH[f"{name}/ref/states"]) < TOL32
@@ -377,7 +414,8 @@ def test_golden_chains(FD, case, path):
         assert nrel(got["dh0"], CH[f"{name}/ref32/dh0"]) < 3e-2
 
 
-def test_config1_full_size(FD):
+@pytest.mark.parametrize("combine", COMBINE_PATHS)
+def test_config1_full_size(FD, combine):
     """benchmark configuration 1 (fp32, 512 tokens, d=768, K=4, R=4, seed 0): every read state against the
     reference's, at the stored tokens and through per-token sums of every state."""
     CFG1 = np.load(os.path.join(G, "cfg1_chain_fp32.npz"))
@@ -386,7 +424,8 @@ def test_config1_full_size(FD):
     assert cases.checksum(h0, D, Q, Gu) == pytest.approx(float(CFG1["checksum"]), rel=1e-12)
     N, n_tok, d = c["K"] * c["R"], c["b"] * c["t"], c["d"]
     for scores in (True, False):
-        got = chain_gpu(FD, h0, D, Q, Gu, c["K"], c["R"], c["beta"], c["eps"], scores=scores, with_grad=False)
+        got = chain_gpu(FD, h0, D, Q, Gu, c["K"], c["R"], c["beta"], c["eps"], scores=scores, with_grad=False,
+                        path=combine)
         st = got["states"].reshape(N, n_tok, d).cpu()
         tok = torch.from_numpy(CFG1["tokens"])
         assert rel(st[:, tok, :], CFG1["states_at_tokens"]) < TOL32
@@ -401,7 +440,8 @@ def test_config1_full_size(FD):
 @pytest.mark.parametrize("write_kernel", [0, 3])      # by size / the tensor-core write where it applies
 @pytest.mark.parametrize("d,K,R,n_tok", [(1024, 4, 6, 96), (1536, 6, 4, 40), (3072, 8, 3, 24), (2048, 5, 4, 64),
                                          (2048, 5, 16, 64)])
-def test_bf16_chain_teacher_forced(FD, L, d, K, R, n_tok, write_kernel):
+@pytest.mark.parametrize("combine", COMBINE_PATHS)
+def test_bf16_chain_teacher_forced(FD, L, d, K, R, n_tok, write_kernel, combine):
     """Each read of a bf16 chain, given the GPU chain's own stored updates, base and installed coefficients,
     against the C oracle's fp32 evaluation of exactly those inputs: <= 2e-2 * RMS(out) max-abs per read."""
     from loopback_b200.cell import LoopDeltaAttnRes
@@ -409,6 +449,7 @@ def test_bf16_chain_teacher_forced(FD, L, d, K, R, n_tok, write_kernel):
     L.set_option("write_tt", write_kernel)
     h0, D, Q, Gu = cases.chain_inputs(1, n_tok, d, K, R, seed=d + K, dtype=torch.bfloat16, sigma_d=0.3)
     cell = LoopDeltaAttnRes(d, R, K, beta=0.75, eps=1e-6).cuda()
+    cell.fuse_prologue = combine == "fused"
     with torch.no_grad():
         cell.query.copy_(Q[:N - 1].cuda())
     stack = cell.new_stack((1, n_tok, d), torch.bfloat16, "cuda", scores=True)
@@ -421,7 +462,11 @@ def test_bf16_chain_teacher_forced(FD, L, d, K, R, n_tok, write_kernel):
             hs = x + D[s].cuda()
             deltas.append(stack.write(s, hs, x))
             cb_in, pr_in = coeffs, prior
-            x_new, coeffs, prior = cell.combine(hs, h0g, deltas, coeffs, prior, l, blk, keys=keys, stack=stack)
+            if combine == "reference_combine":
+                x_new, coeffs, prior = reference_combine(cell, FD, hs, h0g, deltas, coeffs, prior, l, blk, keys=keys,
+                                                         stack=stack)
+            else:
+                x_new, coeffs, prior = cell.combine(hs, h0g, deltas, coeffs, prior, l, blk, keys=keys, stack=stack)
             if s >= 1:
                 base, cbar, c0 = TO.prologue(hs, h0g, cb_in, pr_in, 0.75, blk == K - 1)
                 V = stack.V[:s + 1].float().cpu().numpy().reshape(s + 1, n_tok, d)
@@ -441,11 +486,12 @@ def test_bf16_chain_teacher_forced(FD, L, d, K, R, n_tok, write_kernel):
 @pytest.mark.parametrize("d,K,R,n_tok,dtype", [(768, 4, 4, 50, torch.float32), (1024, 4, 6, 33, torch.float32),
                                                (3072, 2, 3, 11, torch.float32), (64, 5, 16, 3, torch.float32)])
 @pytest.mark.parametrize("scores", [True, False])
-def test_fp32_chain_with_gradients(FD, d, K, R, n_tok, dtype, scores):
+@pytest.mark.parametrize("combine", COMBINE_PATHS)
+def test_fp32_chain_with_gradients(FD, d, K, R, n_tok, dtype, scores, combine):
     """fp32 chains, forward and the gradients of h0, every update and every query, against the C oracle (fp64)."""
     N = K * R
     h0, D, Q, Gu = cases.chain_inputs(1, n_tok, d, K, R, seed=3 * d + N, dtype=dtype, sigma_q=0.1)
-    got = chain_gpu(FD, h0, D, Q, Gu, K, R, 0.75, 1e-6, scores=scores, with_grad=True)
+    got = chain_gpu(FD, h0, D, Q, Gu, K, R, 0.75, 1e-6, scores=scores, with_grad=True, path=combine)
     want = CO.chain(h0.double().numpy().reshape(n_tok, d), D.double().numpy().reshape(N, n_tok, d),
                     Q.double().numpy(), Gu.double().numpy().reshape(N, n_tok, d), K, R, 0.75, 1e-6, False)
     assert rel(got["states"].reshape(N, n_tok, d), want["states"]) < TOL32
@@ -453,6 +499,76 @@ def test_fp32_chain_with_gradients(FD, d, K, R, n_tok, dtype, scores):
     assert rel(got["dq"], want["dq"][:N - 1]) < 3e-5
     assert rel(got["dD"].reshape(N, n_tok, d), want["dD"]) < 3e-5
     assert rel(got["dh0"].reshape(n_tok, d), want["dh0"]) < 3e-5
+
+
+def oracle_chain_grads(h0, D, Q, Gu, K, R, hi, accumulate, scale_grads=True, beta=0.75, eps=1e-6):
+    """The K x R chain in torch on the CPU (blocks x -> x + D_s) with autograd's gradients of sum_s <state_s, G_s>.
+    hi = float64 with accumulate "exact": the chain evaluated exactly on the given (already rounded) inputs;
+    hi = bfloat16 with accumulate "storage": the reference's own bf16 arithmetic, forward and backward.
+    scale_grads=False cuts the gradient through the key scales (a caller that keeps no `keys`)."""
+    ct = torch.float64 if hi == torch.float64 else torch.float32
+    h0r = h0.detach().to(hi).clone().requires_grad_()
+    Dr = D.detach().to(hi).clone().requires_grad_()
+    Qr = Q.detach().to(ct).clone().requires_grad_()
+    N = K * R
+    x, sources, scales, tc, c0, loss, states = h0r, [], [], None, None, 0.0, []
+    for s in range(N):
+        h = x + Dr[s]
+        v = h - x
+        sources.append(v)
+        r = TO.key_scale(v, eps)
+        scales.append(r if scale_grads else r.detach())
+        base, cbar, c0 = TO.prologue(h, h0r, tc, c0, beta, s % K == K - 1)
+        if s == 0:
+            x, tc = base, cbar
+        else:
+            out, tc = TO.read(base, sources, Qr[s - 1], cbar, c0, eps, accumulate=accumulate, scales=scales)
+            x = out.to(hi)
+        states.append(x.detach())
+        loss = loss + (x.to(ct) * Gu[s].to(ct)).sum()
+    loss.backward()
+    return dict(states=torch.stack(states), dq=Qr.grad, dD=Dr.grad, dh0=h0r.grad)
+
+
+@pytest.mark.parametrize("write_kernel", [0, 3])
+@pytest.mark.parametrize("d,K,R,n_tok", [(1024, 4, 6, 160), (1536, 6, 4, 96), (3072, 8, 3, 64), (2048, 5, 4, 64)])
+@pytest.mark.parametrize("combine", COMBINE_PATHS)
+def test_bf16_chain_with_gradients(FD, L, d, K, R, n_tok, write_kernel, combine):
+    """bf16 chains at the benchmark's row widths, through the stack with cached scores: the gradients of every query,
+    every update and h0 against the chain evaluated in fp64 on the same bf16-rounded inputs, no worse than twice the
+    error of the reference's own bf16 arithmetic plus 2e-3 (tests/test_fused_dattn.py:96-108). Covers the
+    accumulating backward with the in-kernel finalisation, one and several warps per token, and the bf16 rounding of
+    the gradient-stack accumulation."""
+    L.set_option("write_tt", write_kernel)
+    h0, D, Q, Gu = cases.chain_inputs(1, n_tok, d, K, R, seed=5 * d + K, dtype=torch.bfloat16, sigma_d=0.3, sigma_q=0.05)
+    got = chain_gpu(FD, h0, D, Q, Gu, K, R, 0.75, 1e-6, scores=True, with_grad=True, path=combine)
+    L.set_option("write_tt", 0)
+    want = oracle_chain_grads(h0, D, Q, Gu, K, R, torch.float64, "exact")
+    ref = oracle_chain_grads(h0, D, Q, Gu, K, R, torch.bfloat16, "storage")
+    N = K * R
+    for k in ("dq", "dD", "dh0"):
+        w = want[k][:N - 1] if k == "dq" else want[k]
+        rf = ref[k][:N - 1] if k == "dq" else ref[k]
+        e_got, e_ref = rel(got[k], w), rel(rf, w)
+        assert e_got <= 2.0 * e_ref + 2e-3, (k, e_got, e_ref)
+    assert torch.isfinite(got["states"].float()).all()
+
+
+@pytest.mark.parametrize("combine", ["dropin", "reference_combine"])
+@pytest.mark.parametrize("scores", [True, False])
+def test_fp32_chain_without_keys(FD, combine, scores):
+    """A caller that passes keys=None (the scales are then plain slices of the stack, without a gradient path):
+    same states; the query and h0 gradients are those of the chain with the key scales held constant. (The
+    updates themselves get no gradient then, in the reference as here: their one gradient is handed out by the
+    scale's node, fused_dattn.py:711-722.)"""
+    d, K, R, n_tok = 256, 3, 3, 21
+    N = K * R
+    h0, D, Q, Gu = cases.chain_inputs(1, n_tok, d, K, R, seed=77, dtype=torch.float32, sigma_q=0.1)
+    got = chain_gpu(FD, h0, D, Q, Gu, K, R, 0.75, 1e-6, scores=scores, with_grad=True, path=combine, use_keys=False)
+    want = oracle_chain_grads(h0, D, Q, Gu, K, R, torch.float64, "exact", scale_grads=False)
+    assert rel(got["states"], want["states"]) < TOL32
+    assert rel(got["dq"], want["dq"][:N - 1]) < 3e-5
+    assert rel(got["dh0"], want["dh0"]) < 3e-5
 
 
 # ------------------------------------------------------------------------------------------------------------
