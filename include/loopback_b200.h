@@ -153,6 +153,24 @@ int lb_combine_bwd(const void *V, const float *R, void *dV, float *dR, const flo
                    const float *LSE0, float *dtc_prev, float *dq, void *scratch, void *neg_out, int finalize,
                    int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream);
 
+/* The backward of one whole step -- the write of update n-1 and the read that follows it -- for callers that make
+ * the two one autograd node: lb_combine_bwd with finalize, handing out the step's own gradients instead of dV[n-1]:
+ *   dx  [n_tok][d] = -dV[n-1]                      the gradient of the block input (the write's x)
+ *   dh  [n_tok][d] = round(dV[n-1] + dbase/dh)     the gradient of the block output: the finished gradient of the
+ *                    update plus what reaches it as the read's base: g inside an iteration (blend == 0); at an
+ *                    iteration's end (blend != 0, base = h + beta (h0 - h)) g - round(beta g), as autograd forms it
+ *   dh0 [n_tok][d] or NULL: the blend's gradient of h0, round(beta g): written when dh0_accum == 0, else added to what
+ *                    dh0 holds with the storage-dtype rounding of an in-place add (a pass's reads, last to first,
+ *                    build the loop input's gradient in one buffer)
+ * dV[n-1] itself is not stored (no later backward reads it); dV[i], dR[i] for i < n-1, dtc_prev and dq as
+ * lb_combine_bwd. Replaces, on top of what lb_combine_bwd replaces, _WriteDelta.backward and the autograd
+ * accumulation of the block output's two gradients (fused_dattn.py:693-695) and the blend's backward
+ * (modeling_looped_transformer.py:148-149). */
+int lb_step_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
+                const float *tc_prev, float lam, const float *c0, const float *LG, const float *LSE, const float *LSE0,
+                float *dtc_prev, float *dq, void *scratch, void *dh, void *dx, void *dh0, int dh0_accum, int blend,
+                float beta, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream);
+
 /* The widest row lb_read_bwd_noalloc accepts. */
 #define LB_NOALLOC_MAX_D 3072
 

@@ -32,6 +32,7 @@ class LoopDeltaAttnRes(nn.Module):
         self.eps = float(eps)
         self.query = nn.Parameter(torch.zeros(self.num_steps - 1, self.dim))
         self.fuse_prologue = True      # fold the boundary blend and the coefficient append/decay into the kernels
+        self.fuse_step = True          # ... and make the write and the read of a step one autograd node
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -88,13 +89,26 @@ class LoopDeltaAttnRes(nn.Module):
             rows = self.prior_rows(proposal.device)
             if prior_coeffs is not None and prior_coeffs.data_ptr() == rows[step - 1].data_ptr():
                 # the whole prologue (boundary blend, appended 1, decay) runs inside the kernels
+                lam = 1.0 - self.beta if closes_iteration else 1.0
+                c0 = rows[step, :step + 1]
+                w = stack._last_write
+                if (self.fuse_step and keys is not None and w is not None and w[0] == step and w[1] is proposal
+                        and len(keys) >= step and (step > 1 or len(keys) >= 1)):
+                    # one autograd node for the step: the write's tensors come from the stack, no update or scale is
+                    # an input (step 1 excepted, which finishes update 0)
+                    stack._last_write = None
+                    if len(keys) < len(deltas):
+                        keys.append(FD._alias(stack.R, step))
+                    first = (deltas[0], keys[0]) if step == 1 else ()
+                    out, tc = FD.FusedStepStk.apply(stack, step, self.query, proposal, w[2],
+                                                    h0 if closes_iteration else None, self.beta, coeffs, lam, c0, *first)
+                    return out, tc, c0
                 if keys is not None and len(keys) < len(deltas):
                     keys.append(stack.rstd(step, deltas[-1], self.eps))
                 scales = keys if keys is not None else [FD._alias(stack.R, i) for i in range(len(deltas))]
-                c0 = rows[step, :step + 1]
                 out, tc = FD.FusedCombineStk.apply(stack, step, self.query[step - 1], proposal,
-                                                   h0 if closes_iteration else None, self.beta, coeffs,
-                                                   1.0 - self.beta if closes_iteration else 1.0, c0, *deltas, *scales)
+                                                   h0 if closes_iteration else None, self.beta, coeffs, lam, c0,
+                                                   *deltas, *scales)
                 return out, tc, c0
         base = proposal + self.beta * (h0 - proposal) if closes_iteration else proposal
         ones_tok = torch.ones(*proposal.shape[:-1], 1, device=proposal.device, dtype=torch.float32)

@@ -420,11 +420,21 @@ static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int q
 
 size_t lb_read_bwd_scratch_bytes(int d) { return d > 0 ? (size_t)kMaxGrid * (size_t)d * sizeof(float) : 0; }
 
+// what a finalising backward hands out beyond dV / dR when the write and the read of update n-1 are one autograd node
+struct StepGrads {
+    void *dh = nullptr;        // gradient of the block output
+    void *dh0 = nullptr;       // gradient of the loop input (an iteration's last read only)
+    int dh0_accum = 0;
+    int blend = 0;
+    float beta = 0.f;
+    int skip_final_store = 0;
+};
+
 static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
                          const float *gt, const float *cbar, const float *tc_prev, float lam, const float *c0,
                          const float *LG, const float *LSE, const float *LSE0, float *dcbar, float *dq, void *scratch,
                          int64_t n_tok, int d, int N, int n, int accum, int finalize, void *neg_out, int dtype,
-                         void *stream);
+                         void *stream, const StepGrads &sg = StepGrads());
 
 int lb_read_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
                 const float *cbar, const float *c0, const float *LG, const float *LSE, const float *LSE0, float *dcbar,
@@ -454,11 +464,27 @@ int lb_read_bwd_final(const void *V, const float *R, void *dV, float *dR, const 
                          accum, 1, neg_out, dtype, stream);
 }
 
+int lb_step_bwd(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g, const float *gt,
+                const float *tc_prev, float lam, const float *c0, const float *LG, const float *LSE, const float *LSE0,
+                float *dtc_prev, float *dq, void *scratch, void *dh, void *dx, void *dh0, int dh0_accum, int blend,
+                float beta, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream) {
+    if (n < 2 || !tc_prev) return fail(LB_ERR_ARG, "lb_step_bwd: needs n >= 2 and the previous read's coefficients");
+    if (!dh || !dx) return fail(LB_ERR_ARG, "lb_step_bwd: dh and dx must be non-NULL");
+    if (!aligned16(dh) || !aligned16(dx) || (dh0 && !aligned16(dh0)))
+        return fail(LB_ERR_ALIGN, "lb_step_bwd: dh, dx and dh0 must be 16-byte aligned");
+    if (dh0 && !blend) return fail(LB_ERR_ARG, "lb_step_bwd: dh0 is only produced by a read that closes an iteration");
+    StepGrads sg;
+    sg.dh = dh; sg.dh0 = dh0; sg.dh0_accum = dh0 ? dh0_accum : 0; sg.blend = blend ? 1 : 0; sg.beta = beta;
+    sg.skip_final_store = 1;
+    return read_bwd_impl(V, R, dV, dR, q, g, gt, nullptr, tc_prev, lam, c0, LG, LSE, LSE0, dtc_prev, dq, scratch, n_tok, d,
+                         N, n, accum, 1, dx, dtype, stream, sg);
+}
+
 static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
                          const float *gt, const float *cbar, const float *tc_prev, float lam, const float *c0,
                          const float *LG, const float *LSE, const float *LSE0, float *dcbar, float *dq, void *scratch,
                          int64_t n_tok, int d, int N, int n, int accum, int finalize, void *neg_out, int dtype,
-                         void *stream) {
+                         void *stream, const StepGrads &sg) {
     int rc = check_common(n_tok, d, dtype);
     if (rc) return rc;
     if (!V || !R || !dV || !dR || !q || !g || (!cbar && !tc_prev) || !c0 || !LG || !LSE || !LSE0 || !dcbar || !dq || !scratch)
@@ -509,10 +535,11 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     if (lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec) > kMaxSmem)
         return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: shared memory does not fit for d=%d, n=%d", d, n);
 
-    CUtensorMap tmV, tmG, tmDV;
+    CUtensorMap tmV, tmG, tmDV, tmH0;
     if ((rc = make_map(&tmV, V, dtype, n_tok, d, N, bt, rank4 ? nch : 0))) return rc;
     if ((rc = make_map(&tmG, g, dtype, n_tok, d, 0, bt, rank4 ? nch : 0))) return rc;
     if ((rc = make_map(&tmDV, dV, dtype, n_tok, d, N, bt, rank4 ? nch : 0))) return rc;
+    if ((rc = make_map(&tmH0, sg.dh0 ? sg.dh0 : g, dtype, n_tok, d, 0, bt, rank4 ? nch : 0))) return rc;
 
     lb::ReadBwdParams p;
     p.R = R; p.dR = dR; p.dV = dV; p.q = q; p.gt = gt; p.cbar = cbar; p.tc_prev = tc_prev; p.lam = lam; p.c0 = c0; p.LSE = LSE; p.LSE0 = LSE0; p.LG = LG;
@@ -520,11 +547,13 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     p.n_tok = n_tok; p.tok_tiles = (n_tok + bt - 1) / bt; p.d = d; p.n = n; p.chunks = nch; p.wpt = wpt;
     p.stages = stages; p.rank4 = rank4 ? 1 : 0; p.accum = accum ? 1 : 0; p.finalize = finalize ? 1 : 0;
     p.neg_out = finalize ? neg_out : nullptr; p.inv_sqrt_d = 1.0f / sqrtf((float)d);
+    p.dh_out = finalize ? sg.dh : nullptr; p.dh0 = finalize ? sg.dh0 : nullptr; p.dh0_accum = sg.dh0_accum;
+    p.blend = sg.blend; p.beta = sg.beta; p.skip_final_store = finalize ? sg.skip_final_store : 0;
     p.err_word = di.err_word;
     int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
     if (cap > kMaxGrid) cap = kMaxGrid;
     const int grid = (int)(p.tok_tiles < cap ? p.tok_tiles : cap);
-    cudaError_t e = lb::launch_read_bwd(dtype, fr, ncw, tmV, tmG, tmDV, p, grid, st);
+    cudaError_t e = lb::launch_read_bwd(dtype, fr, ncw, tmV, tmG, tmDV, tmH0, p, grid, st);
     if (e != cudaSuccess) return cuda_fail(e, "lb_read_bwd launch");
     e = lb::launch_dq_reduce(p.dq_part, grid, dq, d, p.inv_sqrt_d, st);
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_read_bwd dq reduction launch");

@@ -108,13 +108,21 @@ struct ReadBwdParams {
     int accum;             // 0: dV / dR are written; 1: added into
     int finalize;          // 1: also add the key-scale gradient term of source n-1 into dV[n-1] (its last reader)
     void *neg_out;         // [n_tok][d] or null: receives -dV[n-1] when finalize is set
+    // the step's own gradients, with finalize (one autograd node for the write and the read of update n-1):
+    void *dh_out;          // [n_tok][d] or null: dV[n-1] + the gradient of the read's base with respect to the block output
+    void *dh0;             // [n_tok][d] or null: receives (dh0_accum: is added) round(beta g), the blend's h0 gradient
+    int dh0_accum;
+    int blend;             // 1: the read closed an iteration (base = h + beta (h0 - h))
+    float beta;
+    int skip_final_store;  // 1: dV[n-1] itself is not stored (nothing reads it after its last reader)
     float inv_sqrt_d;
     int *err_word;
 };
 
 size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec);
 cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmG,
-                            const CUtensorMap &tmDV, const ReadBwdParams &p, int grid, cudaStream_t stream);
+                            const CUtensorMap &tmDV, const CUtensorMap &tmH0, const ReadBwdParams &p, int grid,
+                            cudaStream_t stream);
 cudaError_t launch_dq_reduce(const float *dq_part, int rows, float *dq, int d, float scale, cudaStream_t stream);
 
 }  // namespace lb

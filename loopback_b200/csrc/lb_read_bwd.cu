@@ -17,6 +17,7 @@
 // 512 B each). Warp roles: NCW consumer warps, 1 TMA producer lane, 2 scalar warps that prepare the
 // per-(token, source) tables of the next tile. The element math runs on pairs (fma.rn.f32x2). All waits are bounded.
 #include <cstddef>
+#include <type_traits>
 
 #include "lb_common.cuh"
 #include "lb_kernels.h"
@@ -55,10 +56,12 @@ size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec)
 
 // SOLO: one warp owns a token's whole row (WPT == 1): no exchange between warps, no named barriers, a one-source-deep
 // pipeline; g stays packed in registers (unpacked where it is used) to leave room for 4 fragments per lane.
-template <typename T, int FR, int NCW, bool SOLO>
+// STEP: the backward of a whole step (lb_step_bwd): always finalising, the newest update's gradient leaves as the
+// gradients of the block output and input instead of being stored.
+template <typename T, int FR, int NCW, bool SOLO, bool STEP>
 __global__ void __launch_bounds__((NCW + 1 + kBwdScalarWarps) * 32, 1)
 read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
-                const __grid_constant__ CUtensorMap tmDV, ReadBwdParams p) {
+                const __grid_constant__ CUtensorMap tmDV, const __grid_constant__ CUtensorMap tmH0, ReadBwdParams p) {
     using S = Store<T>;
     constexpr int VEC = S::kVec;
     constexpr int P = S::kPairs;
@@ -113,7 +116,8 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     __syncthreads();
     const WaitCtx wc{abort_a, p.err_word};
     const long long n_tiles = p.tok_tiles;
-    const int items_per_tile = 1 + n + (p.accum ? n : 0);
+    const bool dh0_rmw = p.dh0 != nullptr && p.dh0_accum != 0;       // the old h0 gradient comes as one more tile
+    const int items_per_tile = 1 + n + (p.accum ? n : 0) + (dh0_rmw ? 1 : 0);
     // stage layout: token-major [t][chunk][512 B] when one 4-D TMA box fills a stage, chunk-major [chunk][t][512 B]
     // when the row is fetched chunk by chunk
     const int tstride = p.rank4 ? p.chunks : 1, cstride = p.rank4 ? 1 : BT;
@@ -168,6 +172,33 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_a + 8u * st);
                 if (++st == NS) { st = 0; ph ^= 1u; }
+            }
+            if (STEP && p.dh0 != nullptr) {
+                // the read closed an iteration (base = h + beta (h0 - h)): h0's share of g, round(beta g), leaves at
+                // once -- written, or added to what earlier backward reads of the pass left there (that tile is the
+                // next item of the ring)
+                uint32_t sb0 = 0;
+                if (dh0_rmw) {
+                    if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                    sb0 = stages_a + (uint32_t)st * kStageBytes;
+                }
+                const float2 b2 = make_float2(p.beta, p.beta);
+#pragma unroll
+                for (int k = 0; k < FR; ++k) {
+                    float2 bg[P];
+                    load_g(k, bg);
+#pragma unroll
+                    for (int e = 0; e < P; ++e) bg[e] = __fmul2_rn(b2, bg[e]);
+                    const uint4 acc0 = dh0_rmw ? S::accum(valid[k] ? lds_v4(sb0 + foff[k]) : zero4, bg) : S::pack2v(bg);
+                    const int col = (chunk0 + k) * BW + lane * VEC;
+                    if (alive && tok_in && col < p.d)
+                        st_global_v4(reinterpret_cast<T *>(p.dh0) + tok * (long long)p.d + col, acc0);
+                }
+                if (dh0_rmw) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                    if (++st == NS) { st = 0; ph ^= 1u; }
+                }
             }
             if (alive && !mbar_wait(sfull_a + 8u * buf, (uint32_t)((tcount >> 1) & 1), wc, kDevWaitScalars)) alive = false;
 
@@ -294,47 +325,118 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     q2[k][2 * e4 + 1] = make_float2(q4.z, q4.w);
                 }
             }
-            T *dvrow = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d + chunk0 * BW + lane * VEC;
-            const long long src_stride = p.n_tok * (long long)p.d;
-            for (int i = 0; i < n; ++i) {
-                const uint32_t i4 = (uint32_t)i * BT4;
-                const float wi = lds_f32(tb + 3u * tfl4 + i4), kq = lds_f32(gk + i4);
-                const float2 w2 = make_float2(wi, wi), kq2 = make_float2(kq, kq);
-                uint4 prev[FR];
-                if (p.accum) {
-                    if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                    const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+            if constexpr (STEP) {
+                T *const dvrow0 = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d + chunk0 * BW + lane * VEC;
+                const long long src_stride = p.n_tok * (long long)p.d;
+                // One source of phase 2. FINAL (compile time) is the newest source of a finalising read. It goes FIRST:
+                // the fragments of that source kept from phase 1 (for its key-scale term) are then dead for the loop
+                // over the older sources, and the loop body carries none of the extra outputs.
+                auto phase2_source = [&](int i, auto final_tag) {
+                    constexpr bool FINAL = decltype(final_tag)::value;
+                    const uint32_t i4 = (uint32_t)i * BT4;
+                    const float wi = lds_f32(tb + 3u * tfl4 + i4), kq = lds_f32(gk + i4);
+                    const float2 w2 = make_float2(wi, wi), kq2 = make_float2(kq, kq);
+                    T *const dvrow = dvrow0 + i * src_stride;
+                    uint4 prev[FR];
+                    if (p.accum) {
+                        if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                        const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(empty_a + 8u * st);
-                    if (++st == NS) { st = 0; ph ^= 1u; }
-                }
-#pragma unroll
-                for (int k = 0; k < FR; ++k) {
-                    float2 o[P], gf[P];
-                    load_g(k, gf);
-#pragma unroll
-                    for (int e = 0; e < P; ++e) o[e] = __ffma2_rn(w2, gf[e], __fmul2_rn(kq2, q2[k][e]));
-                    uint4 res = p.accum ? S::accum(prev[k], o) : S::pack2v(o);
-                    const int col = (chunk0 + k) * BW + lane * VEC;
-                    if (p.finalize && i == n - 1) {
-                        // this read is the last to touch source n-1: add the gradient that reaches the update through
-                        // its key scale, dR (-r^3/d) v, rounded like the separate accumulation kernel would, and hand
-                        // out the negated total (the gradient of the block input)
-                        const float kf = lds_f32(fin_a + t4);
-                        const float2 kf2 = make_float2(kf, kf);
-                        float2 vf[P], kv[P];
-                        S::unpack2(SOLO ? v1[k] : v2[k], vf);
-#pragma unroll
-                        for (int e = 0; e < P; ++e) kv[e] = __fmul2_rn(kf2, vf[e]);
-                        res = S::accum(res, kv);
-                        if (p.neg_out != nullptr && alive && tok_in && col < p.d)
-                            st_global_v4(reinterpret_cast<T *>(p.neg_out) + tok * (long long)p.d + col, S::negate(res));
+                        for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                        if (++st == NS) { st = 0; ph ^= 1u; }
                     }
-                    if (alive && tok_in && col < p.d) st_global_v4(dvrow + k * BW, res);
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) {
+                        float2 o[P], gf[P];
+                        load_g(k, gf);
+#pragma unroll
+                        for (int e = 0; e < P; ++e) o[e] = __ffma2_rn(w2, gf[e], __fmul2_rn(kq2, q2[k][e]));
+                        uint4 res = p.accum ? S::accum(prev[k], o) : S::pack2v(o);
+                        const int col = (chunk0 + k) * BW + lane * VEC;
+                        const bool live = alive && tok_in && col < p.d;
+                        if constexpr (FINAL) {
+                            // this read is the last to touch source n-1: add the gradient that reaches the update through
+                            // its key scale, dR (-r^3/d) v, rounded like the separate accumulation kernel would, and hand
+                            // out the negated total (the gradient of the block input)
+                            const float kf = lds_f32(fin_a + t4);
+                            const float2 kf2 = make_float2(kf, kf);
+                            {
+                                float2 kv[P];
+                                S::unpack2(SOLO ? v1[k] : v2[k], kv);
+#pragma unroll
+                                for (int e = 0; e < P; ++e) kv[e] = __fmul2_rn(kf2, kv[e]);
+                                res = S::accum(res, kv);
+                            }
+                            const long long off = tok * (long long)p.d + col;
+                            if (live) st_global_v4(reinterpret_cast<T *>(p.neg_out) + off, S::negate(res));
+                            {
+                                // the gradient of the block output: the update's finished gradient plus what reaches it as
+                                // the read's base -- g itself inside an iteration; at an iteration's end, where
+                                // base = h + beta (h0 - h), autograd's round(g - round(beta g))
+                                if (p.blend) {
+                                    const float2 b2 = make_float2(p.beta, p.beta);
+                                    float2 bg[P];
+#pragma unroll
+                                    for (int e = 0; e < P; ++e) bg[e] = __fmul2_rn(b2, gf[e]);
+                                    S::unpack2(S::pack2v(bg), bg);                  // rounded to the storage type
+#pragma unroll
+                                    for (int e = 0; e < P; ++e) gf[e] = __fadd2_rn(gf[e], make_float2(-bg[e].x, -bg[e].y));
+                                }
+                                if (live) st_global_v4(reinterpret_cast<T *>(p.dh_out) + off, S::accum(res, gf));
+                            }
+                            // (the finished gradient itself is not stored: no later backward reads it)
+                        } else {
+                            if (live) st_global_v4(dvrow + k * BW, res);
+                        }
+                    }
+                };
+                phase2_source(n - 1, std::true_type{});
+                for (int i = 0; i < n - 1; ++i) phase2_source(i, std::false_type{});
+            } else {
+                T *dvrow = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d + chunk0 * BW + lane * VEC;
+                const long long src_stride = p.n_tok * (long long)p.d;
+                for (int i = 0; i < n; ++i) {
+                    const uint32_t i4 = (uint32_t)i * BT4;
+                    const float wi = lds_f32(tb + 3u * tfl4 + i4), kq = lds_f32(gk + i4);
+                    const float2 w2 = make_float2(wi, wi), kq2 = make_float2(kq, kq);
+                    uint4 prev[FR];
+                    if (p.accum) {
+                        if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                        const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+#pragma unroll
+                        for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                        if (++st == NS) { st = 0; ph ^= 1u; }
+                    }
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) {
+                        float2 o[P], gf[P];
+                        load_g(k, gf);
+#pragma unroll
+                        for (int e = 0; e < P; ++e) o[e] = __ffma2_rn(w2, gf[e], __fmul2_rn(kq2, q2[k][e]));
+                        uint4 res = p.accum ? S::accum(prev[k], o) : S::pack2v(o);
+                        const int col = (chunk0 + k) * BW + lane * VEC;
+                        if (p.finalize && i == n - 1) {
+                            // this read is the last to touch source n-1: add the gradient that reaches the update through
+                            // its key scale, dR (-r^3/d) v, rounded like the separate accumulation kernel would, and hand
+                            // out the negated total (the gradient of the block input)
+                            const float kf = lds_f32(fin_a + t4);
+                            const float2 kf2 = make_float2(kf, kf);
+                            float2 vf[P], kv[P];
+                            S::unpack2(SOLO ? v1[k] : v2[k], vf);
+#pragma unroll
+                            for (int e = 0; e < P; ++e) kv[e] = __fmul2_rn(kf2, vf[e]);
+                            res = S::accum(res, kv);
+                            if (p.neg_out != nullptr && alive && tok_in && col < p.d)
+                                st_global_v4(reinterpret_cast<T *>(p.neg_out) + tok * (long long)p.d + col, S::negate(res));
+                        }
+                        if (alive && tok_in && col < p.d) st_global_v4(dvrow + k * BW, res);
+                    }
+                    dvrow += src_stride;
                 }
-                dvrow += src_stride;
             }
             // the token's warps leave the tile together: gdkq and xch are reused by the next tile
             if (WPT > 1) named_bar_sync(bar_id, bar_threads); else __syncwarp();
@@ -365,6 +467,10 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             tma_prefetch_desc(&tmV);
             tma_prefetch_desc(&tmG);
             if (p.accum) tma_prefetch_desc(&tmDV);
+            if (dh0_rmw) tma_prefetch_desc(&tmH0);
+            const int v0 = dh0_rmw ? 2 : 1;                      // first V item; item 1 is the h0-gradient tile if any
+            // the order in which phase 2 wants the old gradients: a finalising read takes the newest source first
+            auto dv_source = [&](int j) { return STEP ? (j == 0 ? n - 1 : j - 1) : j; };
             int st = 0; uint32_t ph = 0;
             int issued = 0;
             bool ok = true;
@@ -380,14 +486,16 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     mbar_arrive_expect_tx(fb, (uint32_t)(nch * BT * kChunkBytes));
                     if (p.rank4) {
                         if (item == 0) tma_load_3d(sb, &tmG, fb, 0, 0, tok0);
-                        else if (item <= n) tma_load_4d(sb, &tmV, fb, 0, 0, tok0, item - 1);
-                        else tma_load_4d(sb, &tmDV, fb, 0, 0, tok0, item - 1 - n);
+                        else if (item < v0) tma_load_3d(sb, &tmH0, fb, 0, 0, tok0);
+                        else if (item < v0 + n) tma_load_4d(sb, &tmV, fb, 0, 0, tok0, item - v0);
+                        else tma_load_4d(sb, &tmDV, fb, 0, 0, tok0, dv_source(item - v0 - n));
                     } else {
                         for (int c = 0; c < nch; ++c) {
                             const uint32_t dst = sb + (uint32_t)(c * BT * kChunkBytes);
                             if (item == 0) tma_load_2d(dst, &tmG, fb, c * BW, tok0);
-                            else if (item <= n) tma_load_3d(dst, &tmV, fb, c * BW, tok0, item - 1);
-                            else tma_load_3d(dst, &tmDV, fb, c * BW, tok0, item - 1 - n);
+                            else if (item < v0) tma_load_2d(dst, &tmH0, fb, c * BW, tok0);
+                            else if (item < v0 + n) tma_load_3d(dst, &tmV, fb, c * BW, tok0, item - v0);
+                            else tma_load_3d(dst, &tmDV, fb, c * BW, tok0, dv_source(item - v0 - n));
                         }
                     }
                     ++issued;
@@ -444,22 +552,25 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     }
 }
 
-template <typename T, int FR, int NCW, bool SOLO>
+template <typename T, int FR, int NCW, bool SOLO, bool STEP>
 static cudaError_t launch_bwd(const CUtensorMap &tmV, const CUtensorMap &tmG, const CUtensorMap &tmDV,
-                              const ReadBwdParams &p, int grid, cudaStream_t stream) {
+                              const CUtensorMap &tmH0, const ReadBwdParams &p, int grid, cudaStream_t stream) {
     size_t smem = read_bwd_smem_bytes(FR, NCW, p.wpt, p.stages, p.n, Store<T>::kVec);
-    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR, NCW, SOLO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR, NCW, SOLO, STEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    read_bwd_kernel<T, FR, NCW, SOLO><<<grid, (NCW + 1 + kBwdScalarWarps) * 32, smem, stream>>>(tmV, tmG, tmDV, p);
+    read_bwd_kernel<T, FR, NCW, SOLO, STEP><<<grid, (NCW + 1 + kBwdScalarWarps) * 32, smem, stream>>>(tmV, tmG, tmDV, tmH0, p);
     return cudaGetLastError();
 }
 
 cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmG,
-                            const CUtensorMap &tmDV, const ReadBwdParams &p, int grid, cudaStream_t stream) {
+                            const CUtensorMap &tmDV, const CUtensorMap &tmH0, const ReadBwdParams &p, int grid,
+                            cudaStream_t stream) {
     // instantiated shapes. Several warps per token: 16 consumer warps x {1,2} fragments, 12 x {1,2}, 8 x {1,2,3,4};
     // one warp per token (SOLO): 8 x {1,2,3,4}
 #define LB_BWD_CASE(TT, F, W, SOLO_) \
-    if (fr == F && ncw == W && (p.wpt == 1) == SOLO_) return launch_bwd<TT, F, W, SOLO_>(tmV, tmG, tmDV, p, grid, stream);
+    if (fr == F && ncw == W && (p.wpt == 1) == SOLO_)                                                             \
+        return p.dh_out ? launch_bwd<TT, F, W, SOLO_, true>(tmV, tmG, tmDV, tmH0, p, grid, stream)                  \
+                        : launch_bwd<TT, F, W, SOLO_, false>(tmV, tmG, tmDV, tmH0, p, grid, stream);
 #define LB_BWD_ALL(TT)                                                                                         \
     LB_BWD_CASE(TT, 1, 16, false) LB_BWD_CASE(TT, 2, 16, false) LB_BWD_CASE(TT, 1, 12, false)                   \
     LB_BWD_CASE(TT, 2, 12, false) LB_BWD_CASE(TT, 1, 8, false) LB_BWD_CASE(TT, 2, 8, false)                     \

@@ -23,7 +23,7 @@ from . import _lib
 from ._lib import check, dtype_code, ptr, stream_ptr
 
 __all__ = ["rstd", "fused_read_supported", "FusedDattnRead", "DattnStack", "_alias", "FusedDattnReadStk",
-           "FusedCombineStk"]
+           "FusedCombineStk", "FusedStepStk"]
 
 
 def _require_cuda(t: torch.Tensor, what: str) -> None:
@@ -102,7 +102,7 @@ def _launch_read_fwd(V, R, dots, qi, base, cbar, c0, n_tok, d, N, n, save):
         lg = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
         lse = torch.empty(n_tok, device=dev, dtype=torch.float32)
         lse0 = torch.empty(n_tok, device=dev, dtype=torch.float32)
-    with torch.cuda.device(dev), _timed("read_fwd", n):
+    with torch.cuda.device(dev), _timed("read_fwd", n, n + 2):
         check(_lib.lib().lb_read_fwd(ptr(V), ptr(R), ptr(dots), int(qi), ptr(base), ptr(cbar), ptr(c0), ptr(out),
                                      ptr(tc), ptr(lg), ptr(lse), ptr(lse0), n_tok, d, N, n, dtype_code(V.dtype),
                                      stream_ptr()), "read forward")
@@ -114,8 +114,9 @@ def _scratch_for(d: int, device) -> torch.Tensor:
     return torch.empty(nbytes // 4, device=device, dtype=torch.float32)
 
 
-# Optional timing hook: a callable(kind, n, accum) -> context manager wrapped around the big launches; the benchmark
-# installs one that brackets each launch with CUDA events on the launching stream. None = no overhead.
+# Optional timing hook: a callable(kind, n, units) -> context manager wrapped around the big launches; the benchmark
+# installs one that brackets each launch with CUDA events on the launching stream. `units` is the number of
+# [n_tok, d] row-vector transfers the launch makes by design (reads + writes). None = no overhead.
 LAUNCH_TIMER = None
 
 
@@ -127,8 +128,14 @@ class _NoTimer:
         return False
 
 
-def _timed(kind, n, accum=False):
-    return _NoTimer() if LAUNCH_TIMER is None else LAUNCH_TIMER(kind, n, accum)
+def _timed(kind, n, units):
+    return _NoTimer() if LAUNCH_TIMER is None else LAUNCH_TIMER(kind, n, units)
+
+
+def _bwd_units(n, accum, finalize, extra=0):
+    """V once, the gradient stack read + written (written only on a first backward), g in, and with `finalize` the
+    negated copy out."""
+    return n + (2 * n if accum else n) + 1 + (1 if finalize else 0) + extra
 
 
 def _launch_read_bwd(V, R, dV, dR, qc, g, gt, cbar, c0, lg, lse, lse0, scratch, n_tok, d, N, n, accum,
@@ -138,7 +145,7 @@ def _launch_read_bwd(V, R, dV, dR, qc, g, gt, cbar, c0, lg, lse, lse0, scratch, 
     dev = V.device
     dcbar = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
     dq = torch.empty(d, device=dev, dtype=torch.float32)
-    with torch.cuda.device(dev), _timed("read_bwd", n, accum):
+    with torch.cuda.device(dev), _timed("read_bwd", n, _bwd_units(n, accum, finalize)):
         if finalize:
             check(_lib.lib().lb_read_bwd_final(ptr(V), ptr(R), ptr(dV), ptr(dR), ptr(qc), ptr(g), ptr(gt), ptr(cbar),
                                                ptr(c0), ptr(lg), ptr(lse), ptr(lse0), ptr(dcbar), ptr(dq),
@@ -225,7 +232,7 @@ class DattnStack:
     reads that will see it, DOTS[query, update, token] fp32, and the reads use those; the queries are taken as they
     are when the stack is built, i.e. for one forward pass."""
     __slots__ = ("V", "R", "dV", "dR", "n_steps", "n_tok", "d", "eps", "Q", "QT", "DOTS", "r_done", "_scratch",
-                 "fuse_final", "_scale_done", "_neg")
+                 "fuse_final", "_scale_done", "_neg", "_last_write", "_dq", "_dh0", "_first_step", "_first_blend")
 
     def __init__(self, n_steps: int, shape, dtype, device, query=None, eps: float = 1e-6):
         b, t, d = shape
@@ -251,6 +258,12 @@ class DattnStack:
         self.fuse_final = True
         self._scale_done = [False] * self.n_steps
         self._neg = [None] * self.n_steps
+        # Bookkeeping of the one-node-per-step path (FusedStepStk): the tensors of the newest write until the read
+        # that follows it picks them up; the pass's query-gradient rows and loop-input gradient, which the steps'
+        # backward kernels fill in place and the earliest step hands to autograd once.
+        self._last_write = None
+        self._dq = self._dh0 = None
+        self._first_step = self._first_blend = None
         if query is not None:
             self.Q = query.detach().float().contiguous()
             self.DOTS = torch.empty((max(1, self.Q.shape[0]), self.n_steps, b * t), dtype=torch.float32, device=device)
@@ -289,11 +302,12 @@ class _WriteDelta(torch.autograd.Function):
         out = _alias(stack.V, s)
         hc, xc = h.detach().contiguous(), x.detach().contiguous()
         nq = 0 if stack.Q is None else stack.Q.shape[0]
-        with torch.cuda.device(stack.V.device), _timed("write", s):
+        with torch.cuda.device(stack.V.device), _timed("write", s, 3):
             check(_lib.lib().lb_write(ptr(hc), ptr(xc), ptr(stack.V), ptr(stack.R), ptr(stack.Q), ptr(stack.DOTS),
                                       stack.n_tok, stack.d, stack.n_steps, nq, int(s), stack.eps,
                                       dtype_code(stack.V.dtype), stream_ptr()), "write")
         stack.r_done[s] = True
+        stack._last_write = (int(s), h, x)
         ctx.stack, ctx.s = stack, int(s)
         return out
 
@@ -440,7 +454,7 @@ class FusedCombineStk(torch.autograd.Function):
             lg = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
             lse = torch.empty(n_tok, device=dev, dtype=torch.float32)
             lse0 = torch.empty(n_tok, device=dev, dtype=torch.float32)
-        with torch.cuda.device(dev), _timed("read_fwd", n):
+        with torch.cuda.device(dev), _timed("read_fwd", n, n + 2 + (h0 is not None)):
             check(_lib.lib().lb_combine_fwd(ptr(stack.V), ptr(stack.R), ptr(dots), int(qi), ptr(proposal.detach()),
                                             ptr(None if h0 is None else h0.detach()), float(beta), ptr(tcp), float(lam),
                                             ptr(c0c), ptr(out), ptr(tc), ptr(lg), ptr(lse), ptr(lse0), n_tok, d,
@@ -466,7 +480,7 @@ class FusedCombineStk(torch.autograd.Function):
             stack._scale_done[step], stack._neg[step] = True, neg
         dtc = torch.empty((n_tok, n - 1), device=dev, dtype=torch.float32)
         dq = torch.empty(d, device=dev, dtype=torch.float32)
-        with torch.cuda.device(dev), _timed("read_bwd", n, accum):
+        with torch.cuda.device(dev), _timed("read_bwd", n, _bwd_units(n, accum, ctx.finalize)):
             check(_lib.lib().lb_combine_bwd(ptr(stack.V), ptr(stack.R), ptr(stack.dV), ptr(stack.dR), ptr(qc), ptr(g),
                                             ptr(gt_c), ptr(tcp), ctx.lam, ptr(c0c), ptr(lg), ptr(lse), ptr(lse0),
                                             ptr(dtc), ptr(dq), ptr(stack.scratch()), ptr(neg), int(ctx.finalize), n_tok,
@@ -476,6 +490,109 @@ class FusedCombineStk(torch.autograd.Function):
         final = [i == step or (step == 1 and i == 0) for i in range(n)]
         grads = (None, None, dq.to(ctx.q_dtype), dprop, dh0, None, dtc.view(*ctx.shape[:-1], n - 1), None, None,
                  *[None] * n, *[_alias(stack.dR, i) if final[i] else None for i in range(n)])
+        ctx.stack = None
+        return grads
+
+
+class FusedStepStk(torch.autograd.Function):
+    """(out, tc) = apply(stack, step, query, h, x, h0, beta, tc_prev, lam, c0, *first): one autograd node for a whole
+    step -- the write of update `step` (already done by stack.write(step, h, x), whose own node then never runs) and the
+    read that follows it, with the cell's prologue inside the kernels as in FusedCombineStk.
+
+    `query` is the whole (n_steps - 1, d) parameter, `h` / `x` the block's output / input, `h0` the loop input when the
+    read closes an iteration (else None). `first` = (update 0, its key scale) for step 1, which also finishes update 0
+    the way FusedDattnReadStk does; later steps take no update or scale as an input.
+
+    The backward is one kernel plus the reduction of the query-gradient partials. It returns the step's own gradients:
+    dL/dh = (the finished gradient of update `step`) + (the base's gradient), dL/dx = -(the update's gradient), so
+    autograd has nothing to accumulate between the write and the read; the blend's factors are applied in the kernel
+    (dL/dproposal = g - round(beta g), as autograd's own backward of h + beta (h0 - h) gives). Two gradients are built in
+    place over the pass and handed to autograd once, by the earliest step (the last to run): the rows of the query
+    gradient (each step's kernel writes row step - 1) and the loop input's gradient (accumulated in backward order
+    with the storage dtype's rounding, like autograd's own accumulation)."""
+
+    @staticmethod
+    def forward(ctx, stack, step, query, h, x, h0, beta, tc_prev, lam, c0, *first):
+        n = int(step) + 1
+        d, n_tok, dev = stack.d, stack.n_tok, stack.V.device
+        for name, t in (("h", h), ("h0", h0)):
+            if t is not None and (t.dtype != stack.V.dtype or not t.is_contiguous() or t.shape[:-1] != stack.V.shape[1:3]):
+                raise RuntimeError(f"delta_attnres stacked read: {name} must be contiguous, the stack's dtype and shape")
+        if n < 2 or tc_prev is None or tc_prev.shape[-1] != n - 1:
+            raise RuntimeError("delta_attnres stacked read: the previous read's coefficients must have n - 1 entries")
+        c0c = c0.detach().float().contiguous()
+        tcp = tc_prev.detach().float().contiguous()
+        if stack.DOTS is not None and all(stack.r_done[:n]):
+            dots, qi, qc = stack.DOTS, step - 1, stack.Q[step - 1]
+        else:
+            qc = query.detach()[step - 1].float().contiguous()
+            dots, qi = torch.empty((stack.n_steps, n_tok), device=dev, dtype=torch.float32), 0
+            with torch.cuda.device(dev):
+                check(_lib.lib().lb_scores(ptr(stack.V), ptr(qc), ptr(dots), n_tok, d, stack.n_steps, n,
+                                           dtype_code(stack.V.dtype), stream_ptr()), "scores")
+        save = any(ctx.needs_input_grad)
+        out = torch.empty_like(h)
+        tc = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
+        lg = lse = lse0 = None
+        if save:
+            lg = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
+            lse = torch.empty(n_tok, device=dev, dtype=torch.float32)
+            lse0 = torch.empty(n_tok, device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev), _timed("read_fwd", n, n + 2 + (h0 is not None)):
+            check(_lib.lib().lb_combine_fwd(ptr(stack.V), ptr(stack.R), ptr(dots), int(qi), ptr(h.detach()),
+                                            ptr(None if h0 is None else h0.detach()), float(beta), ptr(tcp), float(lam),
+                                            ptr(c0c), ptr(out), ptr(tc), ptr(lg), ptr(lse), ptr(lse0), n_tok, d,
+                                            stack.n_steps, n, dtype_code(stack.V.dtype), stream_ptr()), "combine forward")
+        if save:
+            ctx.save_for_backward(qc, tcp, c0c, lg, lse, lse0)
+            if stack._first_step is None:
+                stack._first_step = int(step)
+            if h0 is not None and ctx.needs_input_grad[5] and stack._first_blend is None:
+                stack._first_blend = int(step)
+        ctx.stack, ctx.step, ctx.n, ctx.shape = stack, int(step), n, h.shape
+        ctx.q_dtype, ctx.q_rows = query.dtype, query.shape[0]
+        ctx.lam, ctx.beta, ctx.blend = float(lam), float(beta), h0 is not None
+        ctx.want_dh0 = bool(h0 is not None and ctx.needs_input_grad[5])
+        ctx.n_first = len(first)
+        return out, tc.view(*h.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, g, gt):
+        qc, tcp, c0c, lg, lse, lse0 = ctx.saved_tensors
+        stack, step, n = ctx.stack, ctx.step, ctx.n
+        d, n_tok, dev = stack.d, stack.n_tok, stack.V.device
+        accum = stack.grads()
+        g = g.contiguous()
+        gt_c = None if gt is None else gt.reshape(n_tok, n).float().contiguous()
+        if stack._dq is None:
+            stack._dq = torch.zeros((ctx.q_rows, d), device=dev, dtype=torch.float32)
+        dh0, dh0_accum = None, False
+        if ctx.want_dh0:
+            dh0_accum = stack._dh0 is not None
+            if not dh0_accum:
+                stack._dh0 = torch.empty(ctx.shape, device=dev, dtype=stack.V.dtype)
+            dh0 = stack._dh0
+        dh = torch.empty(ctx.shape, device=dev, dtype=stack.V.dtype)
+        dx = torch.empty(ctx.shape, device=dev, dtype=stack.V.dtype)
+        dtc = torch.empty((n_tok, n - 1), device=dev, dtype=torch.float32)
+        # V, the older updates' gradients (read + written), g and the newest update's gradient in, dh and dx out, the
+        # loop input's gradient read + written at an iteration's end
+        units = n + ((2 * (n - 1) + 1) if accum else (n - 1)) + 1 + 2 + ((2 if dh0_accum else 1) if dh0 is not None else 0)
+        with torch.cuda.device(dev), _timed("read_bwd", n, units):
+            check(_lib.lib().lb_step_bwd(ptr(stack.V), ptr(stack.R), ptr(stack.dV), ptr(stack.dR), ptr(qc), ptr(g),
+                                         ptr(gt_c), ptr(tcp), ctx.lam, ptr(c0c), ptr(lg), ptr(lse), ptr(lse0), ptr(dtc),
+                                         ptr(stack._dq[step - 1]), ptr(stack.scratch()), ptr(dh), ptr(dx), ptr(dh0),
+                                         int(dh0_accum), int(ctx.blend), ctx.beta, n_tok, d, stack.n_steps, n,
+                                         int(bool(accum)), dtype_code(stack.V.dtype), stream_ptr()), "step backward")
+        dquery = dh0_out = None
+        if step == stack._first_step:             # the earliest step runs last: the pass's query gradient is complete
+            dquery, stack._dq = stack._dq.to(ctx.q_dtype), None
+        if ctx.want_dh0 and step == stack._first_blend:
+            dh0_out, stack._dh0 = stack._dh0, None
+        first = ()
+        if ctx.n_first:                           # step 1 is also the last reader of update 0's key scale
+            first = (None, _alias(stack.dR, 0))
+        grads = (None, None, dquery, dh, dx, dh0_out, None, dtc.view(*ctx.shape[:-1], n - 1), None, None, *first)
         ctx.stack = None
         return grads
 

@@ -154,6 +154,68 @@ def test_read_bwd_final_equals_the_three_separate_kernels(L, dtype, n_tok, d, n,
     assert L.device_error() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_tok,d,n,accum,blend", [(70, 1024, 5, True, True), (33, 1536, 3, False, True),
+                                                   (9, 3072, 4, True, False), (130, 768, 2, True, True),
+                                                   (5, 64, 6, False, False), (64, 2048, 7, True, True),
+                                                   (300, 320, 9, True, True)])
+def test_step_bwd_equals_combine_bwd_plus_the_torch_glue(L, dtype, n_tok, d, n, accum, blend):
+    """lb_step_bwd == lb_combine_bwd (finalising) followed by what autograd does around it: dx is the negated
+    gradient of the update, dh that gradient plus the base's (g, or g - beta g at an iteration's end), dh0 the
+    accumulated beta g. Bit for bit, in the storage dtype's arithmetic."""
+    N, beta, lam = 10, 0.75, 0.25 if blend else 1.0
+    g = torch.Generator(device="cuda").manual_seed(3 * n_tok + d + n)
+    code = L.dtype_code(dtype)
+    V = (torch.randn(N, n_tok, d, device="cuda", generator=g) * 0.5).to(dtype)
+    R = torch.rsqrt(V.float().pow(2).mean(-1) + 1e-6).contiguous()
+    q = (torch.randn(d, device="cuda", generator=g) * 0.3).contiguous()
+    dots = torch.einsum("ntd,d->nt", V.float(), q).contiguous()
+    prop = torch.randn(n_tok, d, device="cuda", generator=g).to(dtype)
+    h0 = torch.randn(n_tok, d, device="cuda", generator=g).to(dtype)
+    c0 = (torch.rand(n, device="cuda", generator=g) * 0.9 + 0.1).contiguous()
+    tcp = (c0[:n - 1].view(1, -1) + 0.2 * torch.randn(n_tok, n - 1, device="cuda", generator=g)).contiguous()
+    out = torch.empty_like(prop)
+    tc, lg = torch.empty(n_tok, n, device="cuda"), torch.empty(n_tok, n, device="cuda")
+    lse, lse0 = torch.empty(n_tok, device="cuda"), torch.empty(n_tok, device="cuda")
+    L.check(L.lib().lb_combine_fwd(L.ptr(V), L.ptr(R), L.ptr(dots), 0, L.ptr(prop), L.ptr(h0) if blend else None, beta,
+                                   L.ptr(tcp), lam, L.ptr(c0), L.ptr(out), L.ptr(tc), L.ptr(lg), L.ptr(lse), L.ptr(lse0),
+                                   n_tok, d, N, n, code, L.stream_ptr()), "fwd")
+    up = torch.randn(n_tok, d, device="cuda", generator=g).to(dtype)
+    gt = torch.randn(n_tok, n, device="cuda", generator=g)
+    dV0 = torch.randn(N, n_tok, d, device="cuda", generator=g).to(dtype)
+    dR0 = torch.randn(N, n_tok, device="cuda", generator=g)
+    dh0_0 = torch.randn(n_tok, d, device="cuda", generator=g).to(dtype)
+    scratch = torch.empty(L.lib().lb_read_bwd_scratch_bytes(d) // 4, device="cuda")
+    head = [L.ptr(V), L.ptr(R)]
+    mid = [L.ptr(q), L.ptr(up), L.ptr(gt), L.ptr(tcp), lam, L.ptr(c0), L.ptr(lg), L.ptr(lse), L.ptr(lse0)]
+    tail = [n_tok, d, N, n, int(accum), code, L.stream_ptr()]
+    dV1, dR1 = dV0.clone(), dR0.clone()
+    dtc1, dq1 = torch.empty(n_tok, n - 1, device="cuda"), torch.empty(d, device="cuda")
+    neg1 = torch.empty(n_tok, d, device="cuda", dtype=dtype)
+    L.check(L.lib().lb_combine_bwd(*head, L.ptr(dV1), L.ptr(dR1), *mid, L.ptr(dtc1), L.ptr(dq1), L.ptr(scratch),
+                                   L.ptr(neg1), 1, *tail), "combine backward")
+    for dh0_accum in ((False, True) if blend else (False,)):
+        dV2, dR2 = dV0.clone(), dR0.clone()
+        dtc2, dq2 = torch.empty(n_tok, n - 1, device="cuda"), torch.empty(d, device="cuda")
+        dh = torch.full((n_tok, d), float("nan"), device="cuda", dtype=dtype)
+        dx = torch.full((n_tok, d), float("nan"), device="cuda", dtype=dtype)
+        dh0 = dh0_0.clone() if dh0_accum else torch.full((n_tok, d), float("nan"), device="cuda", dtype=dtype)
+        L.check(L.lib().lb_step_bwd(*head, L.ptr(dV2), L.ptr(dR2), *mid, L.ptr(dtc2), L.ptr(dq2), L.ptr(scratch),
+                                    L.ptr(dh), L.ptr(dx), L.ptr(dh0) if blend else None, int(dh0_accum), int(blend), beta,
+                                    *tail), "step backward")
+        torch.cuda.synchronize()
+        assert torch.equal(dV1[:n - 1], dV2[:n - 1]) and torch.equal(dR1[:n], dR2[:n])
+        assert torch.equal(dV2[n - 1:], dV0[n - 1:]), "the finished update's gradient is handed out, not stored"
+        assert torch.equal(dtc1, dtc2) and torch.equal(dq1, dq2) and torch.equal(dx, neg1)
+        if blend:
+            bg = up * beta
+            assert torch.equal(dh, dV1[n - 1] + (up - bg))
+            assert torch.equal(dh0, dh0_0 + bg if dh0_accum else bg)
+        else:
+            assert torch.equal(dh, dV1[n - 1] + up)
+    assert L.device_error() == 0
+
+
 # ------------------------------------------------------------------------------------------------------------
 # 2. one read, list layout, in the style of the reference's kernel test (tests/test_fused_dattn.py:48-108)
 # ------------------------------------------------------------------------------------------------------------
@@ -337,10 +399,10 @@ def reference_combine(cell, FD, proposal, h0, deltas, coeffs, prior_coeffs, loop
     return out, target, next_prior
 
 
-# how the chain calls the read: the cell's fast path (prologue inside the kernels, one node per step), the cell with
-# its prologue in torch (FusedDattnReadStk, the entry point the reference trainer calls), the reference's own combine
-# restated above
-COMBINE_PATHS = ["fused", "dropin", "reference_combine"]
+# how the chain calls the read: the cell's fast path (prologue inside the kernels, one autograd node per step:
+# FusedStepStk), the same without the step node (FusedCombineStk), the cell with its prologue in torch
+# (FusedDattnReadStk, the entry point the reference trainer calls), the reference's own combine restated above
+COMBINE_PATHS = ["fused", "fused_combine", "dropin", "reference_combine"]
 
 
 def chain_gpu(FD, h0, D, Q, Gu, K, R, beta, eps, scores, with_grad, list_layout=False, path="fused", use_keys=True):
@@ -349,7 +411,8 @@ def chain_gpu(FD, h0, D, Q, Gu, K, R, beta, eps, scores, with_grad, list_layout=
     N = K * R
     b, t, d = h0.shape
     cell = LoopDeltaAttnRes(d, R, K, beta=beta, eps=eps).cuda()
-    cell.fuse_prologue = path == "fused"
+    cell.fuse_prologue = path in ("fused", "fused_combine")
+    cell.fuse_step = path == "fused"
     with torch.no_grad():
         if N > 1:
             cell.query.copy_(Q[:N - 1].cuda())
@@ -449,7 +512,8 @@ def test_bf16_chain_teacher_forced(FD, L, d, K, R, n_tok, write_kernel, combine)
     L.set_option("write_tt", write_kernel)
     h0, D, Q, Gu = cases.chain_inputs(1, n_tok, d, K, R, seed=d + K, dtype=torch.bfloat16, sigma_d=0.3)
     cell = LoopDeltaAttnRes(d, R, K, beta=0.75, eps=1e-6).cuda()
-    cell.fuse_prologue = combine == "fused"
+    cell.fuse_prologue = combine in ("fused", "fused_combine")
+    cell.fuse_step = combine == "fused"
     with torch.no_grad():
         cell.query.copy_(Q[:N - 1].cuda())
     stack = cell.new_stack((1, n_tok, d), torch.bfloat16, "cuda", scores=True)
