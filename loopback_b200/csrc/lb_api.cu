@@ -37,7 +37,7 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 struct Options {
     int fwd_stages = 0, bwd_stages = 0, fwd_fr = 0, grid_cap = 0, fwd_warps = 0, bwd_warps = 0, bwd_wpt = 0,
-        tma_per_chunk = 0, write_tt = 0, write_mt = 0, fwd_sps = 0;
+        tma_per_chunk = 0, write_tt = 0, write_mt = 0, fwd_sps = 0, write_tile = 0, write_stages = 0;
 } g_opt;
 
 struct DeviceInfo {
@@ -199,6 +199,8 @@ int lb_set_option(const char *name, int value) {
     else if (!strcmp(name, "write_tt")) g_opt.write_tt = value;
     else if (!strcmp(name, "write_mt")) g_opt.write_mt = value;
     else if (!strcmp(name, "fwd_sps")) g_opt.fwd_sps = value;
+    else if (!strcmp(name, "write_tile")) g_opt.write_tile = value;
+    else if (!strcmp(name, "write_stages")) g_opt.write_stages = value;
     else return fail(LB_ERR_ARG, "unknown option '%s'", name);
     return LB_OK;
 }
@@ -237,10 +239,11 @@ int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, fl
         lb::WriteMmaParams mp;
         static_cast<lb::WriteParams &>(mp) = p;
         mp.tile_tok = (int)per * 32;
+        if (g_opt.write_tile >= 32 && g_opt.write_tile <= 256 && g_opt.write_tile % 32 == 0) mp.tile_tok = g_opt.write_tile;
         mp.chunks = (d + 63) / 64;
         mp.n_tiles = (n_tok + mp.tile_tok - 1) / mp.tile_tok;
         mp.err_word = di.err_word;
-        mp.stages = 4;
+        mp.stages = g_opt.write_stages >= 2 && g_opt.write_stages <= 8 ? g_opt.write_stages : 4;
         while (mp.stages > 2 && lb::write_mma_smem_bytes(nt, mp.tile_tok, mp.stages) > 227 * 1024) --mp.stages;
         CUtensorMap tmH, tmX;
         if ((rc = make_map_sw128(&tmH, h, n_tok, d, mp.tile_tok))) return rc;

@@ -41,6 +41,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// (h - x) for two bf16 pairs: the exact difference rounded once to bf16 (the same value as an fp32 subtraction
+// followed by the rounding of a bf16 store)
+__device__ __forceinline__ uint32_t bsub2(uint32_t h, uint32_t x) {
+    const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&h), *reinterpret_cast<const __nv_bfloat162 *>(&x));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+
 // q = hi + mid + lo with three bf16 terms: each remainder is exact in fp32, the third term carries bits 17..24
 __device__ __forceinline__ void split3(float q, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
     const __nv_bfloat16 h = __float2bfloat16_rn(q);
@@ -52,8 +59,9 @@ __device__ __forceinline__ void split3(float q, uint32_t &hi, uint32_t &mid, uin
 }
 
 struct WmBars {
-    unsigned long long full[4], empty[4], qfull[2], qempty[2];
+    unsigned long long full[8], empty[8], qfull[2], qempty[2];
     int abort_flag;
+    int qlow[2][kWmQueryWarps];      // per query buffer and query warp: does the chunk have a non-zero mid or lo term?
 };
 
 // Dynamic shared memory, from a 1024-byte boundary: stages x (h tile | x tile), 2 x 3 query-term blocks of NT x 1024
@@ -75,6 +83,7 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
     const uint32_t full_a = bars_a + offsetof(WmBars, full), empty_a = bars_a + offsetof(WmBars, empty);
     const uint32_t qfull_a = bars_a + offsetof(WmBars, qfull), qempty_a = bars_a + offsetof(WmBars, qempty);
     const uint32_t abort_a = bars_a + offsetof(WmBars, abort_flag);
+    const uint32_t qlow_a = bars_a + offsetof(WmBars, qlow);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NS = p.stages;
@@ -101,15 +110,18 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
         for (long long tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
             const long long tok0 = tile * p.tile_tok;
             float acc[MT][NT > 0 ? NT : 1][4];
-            float ss[2 * MT];
+            // sums of squares of the rounded update, per 16-token tile: [0..1] rows g (the two diagonal candidates of the
+            // rows 0-7 block), [2..3] rows g + 8; only the lane that holds a row's diagonal element uses its value
+            float ss[MT][4];
 #pragma unroll
-            for (int i = 0; i < 2 * MT; ++i) ss[i] = 0.f;
+            for (int mi = 0; mi < MT; ++mi) {
 #pragma unroll
-            for (int mi = 0; mi < MT; ++mi)
+                for (int e = 0; e < 4; ++e) ss[mi][e] = 0.f;
 #pragma unroll
                 for (int nt = 0; nt < (NT > 0 ? NT : 1); ++nt)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) acc[mi][nt][e] = 0.f;
+            }
             for (int c = 0; c < chunks; ++c) {
                 if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
                 if (NT > 0 && alive && !mbar_wait(qfull_a + 8u * qb, qph, wc, kDevWaitScalars)) alive = false;
@@ -119,14 +131,23 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                     // t4 of a 32-column group for rows g and g + 8 of each 16-token tile. Its 8 columns feed two mma
                     // steps (columns 0-3, then 4-7, as the k pairs {2 t4, 2 t4 + 1} and {2 t4 + 8, 2 t4 + 9}); the
                     // query terms are read with the same pattern, so the two operands agree on which column is which k.
-                    float part[MT][NT > 0 ? NT : 1][4];
+                    // The update is formed in bf16 pairs (one exact subtraction, one rounding: what the fp32 route
+                    // gives) and goes to HBM and into the mma as it is. Its squares are summed on the tensor cores as
+                    // well: with B = the A registers of rows 0-7 (8-15) the product's diagonal is sum_k v[r][k]^2.
+                    float part[MT][NT > 0 ? NT : 1][4], sl[MT][4], shh[MT][4];
 #pragma unroll
-                    for (int mi = 0; mi < MT; ++mi)
+                    for (int mi = 0; mi < MT; ++mi) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) { sl[mi][e] = 0.f; shh[mi][e] = 0.f; }
 #pragma unroll
                         for (int nt = 0; nt < (NT > 0 ? NT : 1); ++nt)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) part[mi][nt][e] = 0.f;
+                    }
                     const uint32_t qbase = qs_a + (uint32_t)qb * 3u * kQTerm;
+                    // a chunk whose queries are exact in bf16 (e.g. a bf16 parameter) has zero mid and lo terms
+                    const int terms = NT > 0 ? ((lds_volatile_s32(qlow_a + 8u * qb) | lds_volatile_s32(qlow_a + 8u * qb + 4u)) ? 3 : 1)
+                                             : 0;
 #pragma unroll
                     for (int grp = 0; grp < kWmKC / 32; ++grp) {
                         const uint32_t unit = (uint32_t)(((4 * grp + t4) ^ g) << 4);      // swizzled; row & 7 == g
@@ -138,15 +159,9 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                             for (int hh = 0; hh < 2; ++hh) {
                                 const int r = row0 + 16 * mi + 8 * hh + g;
                                 const uint32_t a = (uint32_t)r * kWmRow + unit;
-                                float hf[8], xf[8];
-                                S::unpack(lds_v4(sh + a), hf);
-                                S::unpack(lds_v4(sx + a), xf);
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) hf[e] = hf[e] - xf[e];
-                                const uint4 packed = S::pack(hf);
-                                S::unpack(packed, hf);
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) ss[2 * mi + hh] = fmaf(hf[e], hf[e], ss[2 * mi + hh]);
+                                const uint4 hv = lds_v4(sh + a), xv = lds_v4(sx + a);
+                                const uint4 packed = make_uint4(bsub2(hv.x, xv.x), bsub2(hv.y, xv.y), bsub2(hv.z, xv.z),
+                                                                bsub2(hv.w, xv.w));
                                 const long long tok = tok0 + r;
                                 if (tok < p.n_tok && col < p.d)
                                     st_global_v4(static_cast<__nv_bfloat16 *>(p.v) + tok * p.d + col, packed);
@@ -154,24 +169,40 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                                 afr[1][mi][hh] = packed.z; afr[1][mi][2 + hh] = packed.w;
                             }
                         }
+#pragma unroll
+                        for (int mi = 0; mi < MT; ++mi) {
+#pragma unroll
+                            for (int ks = 0; ks < 2; ++ks) {
+                                const uint32_t blo[2] = {afr[ks][mi][0], afr[ks][mi][2]};      // rows g as B columns
+                                const uint32_t bhi[2] = {afr[ks][mi][1], afr[ks][mi][3]};      // rows g + 8
+                                mma_bf16(sl[mi], afr[ks][mi], blo);
+                                mma_bf16(shh[mi], afr[ks][mi], bhi);
+                            }
+                        }
                         if (NT > 0) {
 #pragma unroll
                             for (int sp = 2; sp >= 0; --sp) {          // small terms first
+                                if (sp < terms) {
 #pragma unroll
-                                for (int nt = 0; nt < NT; ++nt) {
-                                    const uint4 b = lds_v4(qbase + sp * kQTerm + (uint32_t)(8 * nt + g) * kWmRow + unit);
-                                    const uint32_t b0[2] = {b.x, b.y}, b1[2] = {b.z, b.w};
+                                    for (int nt = 0; nt < NT; ++nt) {
+                                        const uint4 b = lds_v4(qbase + sp * kQTerm + (uint32_t)(8 * nt + g) * kWmRow + unit);
+                                        const uint32_t b0[2] = {b.x, b.y}, b1[2] = {b.z, b.w};
 #pragma unroll
-                                    for (int mi = 0; mi < MT; ++mi) {
-                                        mma_bf16(part[mi][nt], afr[0][mi], b0);
-                                        mma_bf16(part[mi][nt], afr[1][mi], b1);
+                                        for (int mi = 0; mi < MT; ++mi) {
+                                            mma_bf16(part[mi][nt], afr[0][mi], b0);
+                                            mma_bf16(part[mi][nt], afr[1][mi], b1);
+                                        }
                                     }
                                 }
                             }
                         }
                     }
-                    // the chunk's 12 accumulation steps ran in fresh tensor-core accumulators; the running sums are
+                    // the chunk's accumulation steps ran in fresh tensor-core accumulators; the running sums are
                     // round-to-nearest fp32 adds
+#pragma unroll
+                    for (int mi = 0; mi < MT; ++mi) {
+                        ss[mi][0] += sl[mi][0]; ss[mi][1] += sl[mi][1]; ss[mi][2] += shh[mi][2]; ss[mi][3] += shh[mi][3];
+                    }
                     if (NT > 0) {
 #pragma unroll
                         for (int mi = 0; mi < MT; ++mi)
@@ -190,14 +221,16 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                 if (NT > 0) { if (++qb == 2) { qb = 0; qph ^= 1u; } }
             }
             if (active && alive) {
-                // key scales: the 4 lanes of a row group hold the parts of rows g and g + 8 of each 16-token tile
+                // key scales: row g's sum of squares is element (g, g) of the rows 0-7 product, held by lane
+                // t4 == g / 2 in c0 / c1 by g's parity; row g + 8's is element (g + 8, g) of the rows 8-15 product (c2 / c3)
+                if (p.r != nullptr && t4 == (g >> 1)) {
 #pragma unroll
-                for (int i = 0; i < 2 * MT; ++i) {
-                    float s = ss[i];
-                    s += __shfl_xor_sync(0xffffffffu, s, 1);
-                    s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    const long long tok = tok0 + row0 + 16 * (i >> 1) + 8 * (i & 1) + g;
-                    if (t4 == 0 && p.r != nullptr && tok < p.n_tok) p.r[tok] = rsqrtf(s / (float)p.d + p.eps);
+                    for (int mi = 0; mi < MT; ++mi) {
+                        const float s_lo = (g & 1) ? ss[mi][1] : ss[mi][0], s_hi = (g & 1) ? ss[mi][3] : ss[mi][2];
+                        const long long tok = tok0 + row0 + 16 * mi + g;
+                        if (tok < p.n_tok) p.r[tok] = rsqrtf(s_lo / (float)p.d + p.eps);
+                        if (tok + 8 < p.n_tok) p.r[tok + 8] = rsqrtf(s_hi / (float)p.d + p.eps);
+                    }
                 }
                 if (NT > 0) {
                     // scores: accumulator tiles -> [query][token] through shared memory, then 128-byte rows per query
@@ -274,6 +307,7 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                 }
                 if (!mbar_wait<true>(qempty_a + 8u * qb, qph ^ 1u, wc, kDevWaitScalarSlot)) return;
                 const uint32_t qbase = qs_a + (uint32_t)qb * 3u * kQTerm;
+                uint32_t low = 0;
 #pragma unroll
                 for (int it = 0; it < kIter; ++it) {
                     const int idx = ql + 32 * kWmQueryWarps * it;
@@ -281,11 +315,15 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                     uint32_t h0, m0, l0, h1, m1, l1, h2, m2, l2, h3, m3, l3;
                     split3(q4[it].x, h0, m0, l0); split3(q4[it].y, h1, m1, l1);
                     split3(q4[it].z, h2, m2, l2); split3(q4[it].w, h3, m3, l3);
+                    low |= (m0 | m1 | m2 | m3 | l0 | l1 | l2 | l3) & 0x7fffu;       // a term that is not +-0
                     const uint32_t a = qbase + (uint32_t)j * kWmRow + (uint32_t)((((u4 >> 1) ^ (j & 7)) << 4) + (u4 & 1) * 8);
                     sts_v2(a, h0 | (h1 << 16), h2 | (h3 << 16));
                     sts_v2(a + kQTerm, m0 | (m1 << 16), m2 | (m3 << 16));
                     sts_v2(a + 2u * kQTerm, l0 | (l1 << 16), l2 | (l3 << 16));
                 }
+                low = __any_sync(0xffffffffu, low != 0u) ? 1u : 0u;
+                if (lane == 0) sts_s32(qlow_a + 8u * qb + 4u * (uint32_t)(warp - kWmConsumers - 1), (int)low);
+                __syncwarp();
                 mbar_arrive(qfull_a + 8u * qb);
                 if (++qb == 2) { qb = 0; qph ^= 1u; }
             }

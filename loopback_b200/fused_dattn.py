@@ -162,11 +162,64 @@ def _launch_read_bwd(V, R, dV, dR, qc, g, gt, cbar, c0, lg, lse, lse0, scratch, 
 # --------------------------------------------------------------------------------------------------------------
 # list layout: one tensor per source                                reference: fused_dattn.py:264-334
 # --------------------------------------------------------------------------------------------------------------
+class _ListStack:
+    """The list layout's hidden stack. The kernels index ONE array of sources; a caller of the list layout holds one
+    tensor per source and passes the same growing list read after read (the port model's loop). Instead of gathering
+    all n sources again at every read, the sources seen so far are kept here: a read copies only the ones it has not
+    seen (normally one, the newest), so a pass makes N row copies, not N^2 / 2. A slot is valid while the caller's
+    tensor still has the address and the version it had when it was copied; anything else starts a new stack.
+    Dropped when the first source is garbage-collected (the caller's pass is over) -- reads that still need it for
+    their backward hold their own reference."""
+    __slots__ = ("V", "R", "tags", "__weakref__")
+
+    def __init__(self, cap, n_tok, d, dtype, device):
+        self.V = torch.empty((cap, n_tok, d), dtype=dtype, device=device)
+        self.R = torch.empty((cap, n_tok), dtype=torch.float32, device=device)
+        self.tags = []                        # per filled slot: (value ptr, value version, scale ptr, scale version)
+
+    @staticmethod
+    def tag(v, r):
+        return (v.data_ptr(), v._version, r.data_ptr(), r._version)
+
+
+_LIST_STACKS = {}                             # (address of the first source, shape, dtype) -> _ListStack
+
+
+def _list_stack(values, rstds):
+    import weakref
+    v0 = values[0]
+    n, d = len(values), v0.shape[-1]
+    n_tok = v0.numel() // d
+    key = (v0.data_ptr(), tuple(v0.shape), v0.dtype, v0.device)
+    ls = _LIST_STACKS.get(key)
+    tags = [_ListStack.tag(v, r) for v, r in zip(values, rstds)]
+    if ls is not None and (len(ls.tags) > n or ls.tags != tags[:len(ls.tags)]):
+        ls = None                             # not the list this stack was built from
+    if ls is None or ls.V.shape[0] < n:
+        cap = max(8, 2 * n) if ls is not None else max(4, n)
+        grown = _ListStack(min(cap, _lib.LB_MAX_SOURCES), n_tok, d, v0.dtype, v0.device)
+        if ls is not None:
+            k = len(ls.tags)
+            grown.V[:k].copy_(ls.V[:k])
+            grown.R[:k].copy_(ls.R[:k])
+            grown.tags = list(ls.tags)
+        ls = grown
+        _LIST_STACKS[key] = ls
+        weakref.finalize(v0, lambda k=key, ref=weakref.ref(ls): _LIST_STACKS.pop(k, None)
+                         if _LIST_STACKS.get(k) is ref() else None)
+    for i in range(len(ls.tags), n):
+        ls.V[i].copy_(values[i].detach().reshape(n_tok, d))
+        ls.R[i].copy_(rstds[i].detach().reshape(n_tok))
+        ls.tags.append(tags[i])
+    return ls
+
+
 class FusedDattnRead(torch.autograd.Function):
     """(out, tc) = FusedDattnRead.apply(q, base, cbar, c0, *values, *rstds).
 
-    The kernels index one stack, so the n sources are gathered into a temporary stack first (one extra copy of the
-    sources per read; the stacked layout below avoids it and is the path the trainer uses)."""
+    The kernels index one stack; the list's sources are kept in a hidden one that persists from read to read, so each
+    source is copied once per pass (see _ListStack). The stacked layout below needs no copy at all and accumulates
+    the sources' gradients in the kernels; it is the path the trainer uses."""
 
     @staticmethod
     def forward(ctx, q, base, cbar, c0, *srcs):
@@ -179,35 +232,37 @@ class FusedDattnRead(torch.autograd.Function):
         d = v0.shape[-1]
         n_tok = v0.numel() // d
         dev = v0.device
-        Vt = torch.stack([v.detach() for v in values])                       # [n, ..., d]
-        Rt = torch.stack([r.detach().reshape(n_tok) for r in rstds])         # [n, n_tok]
+        ls = _list_stack(values, rstds)
+        N = ls.V.shape[0]
         qc = q.detach().float().contiguous()
         c0c = c0.detach().float().contiguous()
         base_c = base.detach().contiguous()
-        dots = torch.empty((n, n_tok), device=dev, dtype=torch.float32)
+        dots = torch.empty((N, n_tok), device=dev, dtype=torch.float32)
         with torch.cuda.device(dev):
-            check(_lib.lib().lb_scores(ptr(Vt), ptr(qc), ptr(dots), n_tok, d, n, n, dtype_code(Vt.dtype),
+            check(_lib.lib().lb_scores(ptr(ls.V), ptr(qc), ptr(dots), n_tok, d, N, n, dtype_code(ls.V.dtype),
                                        stream_ptr()), "scores")
         save = any(ctx.needs_input_grad)         # no graph (inference): the backward's saves are not written
-        out, tc, lg, lse, lse0 = _launch_read_fwd(Vt, Rt, dots, 0, base_c, cbar_c, c0c, n_tok, d, n, n, save=save)
+        out, tc, lg, lse, lse0 = _launch_read_fwd(ls.V, ls.R, dots, 0, base_c, cbar_c, c0c, n_tok, d, N, n, save=save)
         if save:
-            ctx.save_for_backward(qc, cbar_c, c0c, lg, lse, lse0, Vt, Rt)
+            ctx.save_for_backward(qc, cbar_c, c0c, lg, lse, lse0)
+            ctx.ls = ls           # not a saved tensor: later reads append to the same stack (slots below n never change)
         ctx.n, ctx.q_dtype, ctx.base_shape = n, q.dtype, base.shape
         ctx.rshape = rstds[0].shape
         return out, tc.view(*base.shape[:-1], n)
 
     @staticmethod
     def backward(ctx, g, gt):
-        qc, cbar_c, c0c, lg, lse, lse0, Vt, Rt = ctx.saved_tensors
-        n = ctx.n
-        d = Vt.shape[-1]
-        n_tok = Vt[0].numel() // d
+        qc, cbar_c, c0c, lg, lse, lse0 = ctx.saved_tensors
+        ls, n = ctx.ls, ctx.n
+        ctx.ls = None
+        N, n_tok, d = ls.V.shape
         g = g.contiguous()
         gt_c = None if gt is None else gt.reshape(n_tok, n).float().contiguous()
-        dVt = torch.empty_like(Vt)
-        dRt = torch.empty_like(Rt)
-        scratch = _scratch_for(d, Vt.device)
-        dq, dcbar = _launch_read_bwd(Vt, Rt, dVt, dRt, qc, g, gt_c, cbar_c, c0c, lg, lse, lse0, scratch, n_tok, d, n, n,
+        # the gradients of this read's sources: a private stack with the hidden stack's slice pitch
+        dVt = torch.empty((n,) + tuple(ctx.base_shape), dtype=ls.V.dtype, device=ls.V.device)
+        dRt = torch.empty((n, n_tok), dtype=torch.float32, device=ls.V.device)
+        scratch = _scratch_for(d, ls.V.device)
+        dq, dcbar = _launch_read_bwd(ls.V, ls.R, dVt, dRt, qc, g, gt_c, cbar_c, c0c, lg, lse, lse0, scratch, n_tok, d, N, n,
                                      accum=False)
         return (dq.to(ctx.q_dtype), g, dcbar.view(*ctx.base_shape[:-1], n), None,
                 *dVt.unbind(0), *[dRt[i].view(ctx.rshape) for i in range(n)])

@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--first", action="store_true", help="backward: the pass's first backward (gradients written, not added)")
     ap.add_argument("--blend", action="store_true", help="the read closes an iteration (base blended with h0)")
     ap.add_argument("--bf16-queries", action="store_true", help="write: queries exactly representable in bf16")
+    ap.add_argument("--no-scores", action="store_true", help="write: no queries (update and key scale only)")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--opt", action="append", default=[], help="library tuning knob name=value (lb_set_option)")
     a = ap.parse_args()
@@ -65,8 +66,8 @@ def main():
         units, label = 3, f"write step {a.step}: {NQ - max(a.step - 1, 0)} queries scored"
 
         def launch():
-            L.check(lib.lb_write(L.ptr(h), L.ptr(x), L.ptr(V), L.ptr(R), L.ptr(Q), L.ptr(DOTS), T, d, N, NQ, a.step, 1e-6,
-                                 code, st), "write")
+            L.check(lib.lb_write(L.ptr(h), L.ptr(x), L.ptr(V), L.ptr(R), None if a.no_scores else L.ptr(Q), L.ptr(DOTS), T, d, N,
+                                 NQ, a.step, 1e-6, code, st), "write")
     else:
         DOTS = rnd(N, T, scale=1.0, dtype=torch.float32)                                 # one query's block of scores
         c0 = (torch.rand(n, device=dev, generator=g) * 0.9 + 0.1).contiguous()

@@ -63,12 +63,19 @@ def cuda(x):
 @pytest.mark.parametrize("n_tok,d,N", [(5, 64, 6), (37, 768, 6), (130, 1024, 6), (33, 1536, 6), (9, 3072, 6),
                                        (64, 2048, 6), (19, 512, 70), (5000, 320, 6), (40000, 136, 4),
                                        (300, 4096, 3), (700, 1024, 40)])
-def test_write_matches_oracle(L, dtype, n_tok, d, N, tile):
+@pytest.mark.parametrize("q_in_bf16", [False, True])
+def test_write_matches_oracle(L, dtype, n_tok, d, N, tile, q_in_bf16):
+    """q_in_bf16: queries that are exact in bf16 (a bf16 parameter): the tensor-core kernel then needs one of its
+    three query terms only, and finds that out by itself."""
+    if q_in_bf16 and not (tile == 3 and dtype == torch.bfloat16):
+        pytest.skip("only the tensor-core kernel treats bf16-exact queries specially")
     NQ = N - 1
     L.set_option("write_tt", tile)
     g = torch.Generator().manual_seed(n_tok * 7 + d)
     x = torch.randn(n_tok, d, generator=g).to(dtype)
     Q = torch.randn(NQ, d, generator=g) * 0.3
+    if q_in_bf16:
+        Q = Q.bfloat16().float()
     code = L.dtype_code(dtype)
     V = torch.zeros(N, n_tok, d, dtype=dtype, device="cuda")
     R = torch.zeros(N, n_tok, device="cuda")
@@ -295,6 +302,33 @@ def test_read_bf16_against_fp64(FD, b, t, d, n):
     rms = float(out_tf.pow(2).mean().sqrt())
     err_out = float((got["out"].double().cpu() - out_tf).abs().max())
     assert err_out <= 2e-2 * rms, (err_out, rms)
+    assert rel(got["tc"], want["tc"]) < 1e-4
+    for k in want:
+        if float(want[k].abs().max()) == 0.0:
+            continue
+        e_got, e_ref = rel(got[k], want[k]), rel(ref_bf16[k], want[k])
+        assert e_got <= 2.0 * e_ref + 2e-3, (k, e_got, e_ref)
+
+
+@pytest.mark.parametrize("b,t,d,n,dtype", [(1, 9, 4096, 5, torch.float32), (1, 9, 8192, 5, torch.bfloat16),
+                                           (1, 11, 6144, 3, torch.bfloat16), (1, 40, 1024, 128, torch.float32),
+                                           (1, 40, 1024, 128, torch.bfloat16), (2, 20, 2048, 96, torch.bfloat16)])
+def test_read_at_the_limits(FD, b, t, d, n, dtype):
+    """The widest rows the library takes (16 KiB: 32 chunks, sixteen warps per token in the backward) and the most
+    sources (LB_MAX_SOURCES = 128: four passes of the scalar warps), forward and every gradient."""
+    ins = cases.read_inputs(b, t, d, n, dtype, seed=3 * n + d)
+    got = run_read_gpu(FD, *ins, True)
+    want = run_read_oracle(*ins, True, torch.float64, "exact")
+    if dtype == torch.float32:
+        for k in want:
+            if float(want[k].abs().max()) == 0.0:
+                continue
+            assert rel(got[k], want[k]) < 2e-5, (k, rel(got[k], want[k]))
+        return
+    ref_bf16 = run_read_oracle(*ins, True, torch.bfloat16, "storage")
+    out_tf, _ = teacher_forced_out(ins, True)
+    rms = float(out_tf.pow(2).mean().sqrt())
+    assert float((got["out"].double().cpu() - out_tf).abs().max()) <= 2e-2 * rms
     assert rel(got["tc"], want["tc"]) < 1e-4
     for k in want:
         if float(want[k].abs().max()) == 0.0:
@@ -703,13 +737,14 @@ def test_error_behaviour(FD):
 # ------------------------------------------------------------------------------------------------------------
 # 6. full-size properties (benchmark configuration 2 shapes: 32768 tokens, d=1024, bf16, N=24)
 # ------------------------------------------------------------------------------------------------------------
-def test_full_size_properties(FD):
-    """At configuration 2's size the oracle is too slow, so the checks are properties: (a) per-token independence --
+@pytest.mark.parametrize("d,K,R,b,t", [(1024, 4, 6, 8, 4096), (1536, 6, 4, 16, 4096), (3072, 8, 3, 4, 4096)],
+                         ids=["cfg2", "cfg3", "cfg4_rows_16384_tokens"])
+def test_full_size_properties(FD, d, K, R, b, t):
+    """At configuration 2's and 3's sizes the oracle is too slow, so the checks are properties: (a) per-token independence --
     the chain on the first 8192 tokens alone (still a batch the tensor-core write takes, with other tile sizes in all
     three kernels) reproduces the slice of the full chain bit for bit; (b) the tracked
     coefficients of every token sum to the read's mass; (c) zero queries reduce the chain to the decay-only closed
     form h0 + sum_i lambda^(R - floor(i/K)) D_i (within the bf16 state rounding), and tc == c0 bitwise."""
-    d, K, R, b, t = 1024, 4, 6, 8, 4096
     N = K * R
     g = torch.Generator(device="cuda").manual_seed(0)
     h0 = torch.randn(b, t, d, device="cuda", generator=g).bfloat16()

@@ -57,7 +57,8 @@ def test_noalloc_matches_read_bwd_twice_in_a_row(dtype):
     import loopback_b200._lib as L
     N = 6
     # two different problems back to back: the second call must not see anything of the first in the shared scratch
-    for n_tok, d, n, accum, seed in ((300, 1024, 6, False, 1), (77, 768, 4, True, 2)):
+    # (the last problem runs at the widest row the entry point takes, LB_NOALLOC_MAX_D)
+    for n_tok, d, n, accum, seed in ((300, 1024, 6, False, 1), (77, 768, 4, True, 2), (41, 3072, 5, True, 3)):
         pr = _problem(L, n_tok, d, N, n, dtype, seed)
         g = torch.Generator(device="cuda").manual_seed(100 + seed)
         dV0 = torch.randn(N, n_tok, d, device="cuda", generator=g).to(dtype)
