@@ -112,6 +112,21 @@ int lb_read_fwd(const void *V, const float *R, const float *DOTS, int qi, const 
                 const float *c0, void *out, float *TC, float *LG, float *LSE, float *LSE0, int64_t n_tok, int d, int N,
                 int n, int dtype, void *stream);
 
+/* One whole forward step in one launch, for decode-sized batches (tens to hundreds of tokens, where a step is bound by
+ * launches, not bytes): the write of update s = what lb_write(h, x, ..., s) stores in V[s] and R[s], and the read that
+ * follows it = lb_combine_fwd with n = s + 1 and the query row s - 1 of Q [N-1][d], the new update never leaving the
+ * chip in between. No cached scores are needed or written (DOTS is not an argument): the stored updates, which at
+ * these sizes live in L2, are swept twice, once for the scores and once for the weighted sum. Results agree
+ * with lb_write + lb_combine_fwd to fp32 round-off (another summation order); V[s] is bit-identical; a zero query
+ * with cbar == c0 gives out == base and TC == c0 bit for bit. One CTA per token: use it for batches that cannot fill
+ * the GPU with token tiles. h0 == NULL: base = h; else base = h + beta (h0 - h) as in lb_combine_fwd.
+ * Replaces the reference's per-step pair DattnStack.write + FusedDattnReadStk.forward with their kernels
+ * _write_stk_kernel and _dattn_fwd_stk_kernel (fused_dattn.py:561-585, :410-456, :663-691, :729-759), called back to
+ * back by the model (modeling_looped_transformer.py:472-481). */
+int lb_step_fwd(const void *h, const void *x, const void *h0, float beta, void *V, float *R, const float *Q,
+                const float *tc_prev, float lam, const float *c0, void *out, float *TC, float *LG, float *LSE, float *LSE0,
+                int64_t n_tok, int d, int N, int s, float eps, int dtype, void *stream);
+
 /* Bytes of scratch lb_read_bwd needs for the per-CTA partial rows of the query gradient (depends on d only). */
 size_t lb_read_bwd_scratch_bytes(int d);
 

@@ -31,6 +31,8 @@ SYMBOLS = {
     "lb_rstd_bwd_acc": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _vp]),
     "lb_scores": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp]),
     "lb_read_fwd": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp]),
+    "lb_step_fwd": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _f, _i,
+                         _vp]),
     "lb_read_bwd_scratch_bytes": (ctypes.c_size_t, [_i]),
     "lb_read_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
                          _i, _i, _vp]),

@@ -54,17 +54,29 @@ class LoopDeltaAttnRes(nn.Module):
                 if s % self.num_blocks == self.num_blocks - 1:
                     c = (np.float32(1.0 - self.beta) * c).astype(np.float32)
                 table[s, :s + 1] = c
-            cache[key] = (torch.from_numpy(table).to(device), float(self.beta))
+            rows = torch.from_numpy(table).to(device)
+            # per read: the prior row's address (how combine recognises a prior it handed out) and the row itself
+            cache[key] = (rows, float(self.beta), [rows[s].data_ptr() for s in range(N)],
+                          [rows[s, :s + 1] for s in range(N)])
         if cache[key][1] != float(self.beta):
             del cache[key]
             return self.prior_rows(device)
         return cache[key][0]
 
-    def new_stack(self, shape, dtype, device, scores: bool = True) -> FD.DattnStack:
+    def _prior_views(self, device):
+        self.prior_rows(device)
+        entry = self.__dict__["_prior_cache"][str(torch.device(device))]
+        return entry[2], entry[3]
+
+    def new_stack(self, shape, dtype, device, scores: bool = True, fuse_decode: bool = True) -> FD.DattnStack:
         """The per-forward storage the model creates before its loop over the shared blocks (the trainer model's
-        forward does this inline); `scores` caches each update's scores at its write (LOOP_DATTN_DOTS)."""
-        return FD.DattnStack(self.num_steps, tuple(shape), dtype, device, query=self.query if scores else None,
-                             eps=self.eps)
+        forward does this inline); `scores` caches each update's scores at its write (LOOP_DATTN_DOTS).
+        `fuse_decode`: for decode-sized batches without autograd, a write is launched together with the read that
+        follows it, as one kernel (see DattnStack.defer_writes)."""
+        stack = FD.DattnStack(self.num_steps, tuple(shape), dtype, device, query=self.query if scores else None,
+                              eps=self.eps)
+        stack.defer_writes = bool(fuse_decode and scores)
+        return stack
 
     def combine(self, proposal, h0, deltas, coeffs, prior_coeffs, loop_idx, block_idx, keys=None, stack=None):
         """One read after application `block_idx` of iteration `loop_idx`.
@@ -86,11 +98,20 @@ class LoopDeltaAttnRes(nn.Module):
         closes_iteration = block_idx == self.num_blocks - 1
         if self.fuse_prologue and stack is not None and step >= 1 and coeffs is not None and proposal.is_contiguous() \
                 and (not closes_iteration or h0.is_contiguous()):
-            rows = self.prior_rows(proposal.device)
-            if prior_coeffs is not None and prior_coeffs.data_ptr() == rows[step - 1].data_ptr():
+            row_ptrs, row_views = self._prior_views(proposal.device)
+            if prior_coeffs is not None and prior_coeffs.data_ptr() == row_ptrs[step - 1]:
                 # the whole prologue (boundary blend, appended 1, decay) runs inside the kernels
                 lam = 1.0 - self.beta if closes_iteration else 1.0
-                c0 = rows[step, :step + 1]
+                c0 = row_views[step]
+                pend = stack._pending
+                if (pend is not None and pend[0] == step and pend[1] is proposal and coeffs.dtype == torch.float32
+                        and coeffs.is_contiguous() and not torch.is_grad_enabled()):
+                    # decode-sized batch, no autograd: the recorded write and this read are one launch
+                    if keys is not None and len(keys) < len(deltas):
+                        keys.append(stack.R[step])
+                    out, tc = stack.step_forward(step, proposal, pend[2], h0 if closes_iteration else None, self.beta,
+                                                 coeffs, lam, c0)
+                    return out, tc.view(*proposal.shape[:-1], step + 1), c0
                 w = stack._last_write
                 if (self.fuse_step and keys is not None and w is not None and w[0] == step and w[1] is proposal
                         and len(keys) >= step and (step > 1 or len(keys) >= 1)):

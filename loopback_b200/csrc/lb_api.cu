@@ -421,6 +421,37 @@ static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int q
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_read_fwd launch");
 }
 
+int lb_step_fwd(const void *h, const void *x, const void *h0, float beta, void *V, float *R, const float *Q,
+                const float *tc_prev, float lam, const float *c0, void *out, float *TC, float *LG, float *LSE, float *LSE0,
+                int64_t n_tok, int d, int N, int s, float eps, int dtype, void *stream) {
+    int rc = check_common(n_tok, d, dtype);
+    if (rc) return rc;
+    if (!h || !x || !V || !R || !Q || !tc_prev || !c0 || !out || !TC) return fail(LB_ERR_ARG, "lb_step_fwd: NULL pointer");
+    if ((LG != nullptr) != (LSE != nullptr) || (LG != nullptr) != (LSE0 != nullptr))
+        return fail(LB_ERR_ARG, "lb_step_fwd: LG, LSE and LSE0 must be given together");
+    if (s < 1 || s >= N) return fail(LB_ERR_ARG, "lb_step_fwd: step %d outside [1, N=%d)", s, N);
+    if (s + 1 > LB_MAX_SOURCES) return fail(LB_ERR_UNSUPPORTED, "lb_step_fwd: %d sources exceed LB_MAX_SOURCES=%d", s + 1, LB_MAX_SOURCES);
+    if (!aligned16(h) || !aligned16(x) || !aligned16(V) || !aligned16(out) || !aligned16(Q) || (h0 && !aligned16(h0)))
+        return fail(LB_ERR_ALIGN, "lb_step_fwd: h, x, h0, V, out and Q must be 16-byte aligned");
+    if (((long long)d * 4) % 16) return fail(LB_ERR_ALIGN, "lb_step_fwd: the query rows must be multiples of 16 bytes");
+    if (n_tok > 65535LL * 16) return fail(LB_ERR_UNSUPPORTED, "lb_step_fwd: meant for decode-sized batches; %lld tokens is not one", (long long)n_tok);
+    if (n_tok == 0) return LB_OK;
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    const int elem = dtype == LB_DTYPE_BF16 ? 2 : 4;
+    lb::StepSmallParams p;
+    p.h = h; p.x = x; p.h0 = h0; p.V = V; p.R = R; p.q = Q + (long long)(s - 1) * d; p.tc_prev = tc_prev; p.c0 = c0;
+    p.out = out; p.TC = TC; p.LG = LG; p.LSE = LSE; p.LSE0 = LSE0;
+    p.n_tok = n_tok; p.d = d; p.n = s + 1; p.lam = lam; p.beta = beta; p.eps = eps; p.inv_sqrt_d = 1.0f / sqrtf((float)d);
+    p.blend = h0 ? 1 : 0;
+    const int frags = (d * elem + 15) / 16;
+    p.ct = (frags + 31) / 32 * 32;
+    p.sg = p.ct >= 1024 ? 1 : (1024 / p.ct > 4 ? 4 : 1024 / p.ct);
+    if (lb::step_small_smem_bytes(p.ct, p.sg, 16 / elem) > kMaxSmem) return fail(LB_ERR_UNSUPPORTED, "lb_step_fwd: row too wide");
+    cudaError_t e = lb::launch_step_small(dtype, p, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_step_fwd launch");
+}
+
 size_t lb_read_bwd_scratch_bytes(int d) { return d > 0 ? (size_t)kMaxGrid * (size_t)d * sizeof(float) : 0; }
 
 // what a finalising backward hands out beyond dV / dR when the write and the read of update n-1 are one autograd node

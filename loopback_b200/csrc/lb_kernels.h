@@ -82,6 +82,25 @@ cudaError_t launch_rstd_bwd(int dtype, const void *x, const float *r, const floa
                             int d, int mode, int sms, cudaStream_t stream);
 cudaError_t launch_neg(int dtype, const void *g, void *out, long long n_elem, int sms, cudaStream_t stream);
 
+// One whole forward step for decode-sized batches (lb_step_fwd): one CTA per token, ct column threads x sg source groups
+struct StepSmallParams {
+    const void *h, *x, *h0;   // [n_tok][d]; h0 only when blend
+    void *V;                  // [N][n_tok][d]: slice n-1 is written, slices below are read
+    float *R;                 // [N][n_tok]
+    const float *q;           // [d] the read's query (row n-2 of the queries)
+    const float *tc_prev;     // [n_tok][n-1]
+    const float *c0;          // [n]
+    void *out;                // [n_tok][d]
+    float *TC, *LG, *LSE, *LSE0;
+    long long n_tok;
+    int d, n;
+    float lam, beta, eps, inv_sqrt_d;
+    int blend;
+    int ct, sg;
+};
+size_t step_small_smem_bytes(int ct, int sg, int vec);
+cudaError_t launch_step_small(int dtype, const StepSmallParams &p, cudaStream_t stream);
+
 struct ReadBwdParams {
     const float *R;        // [N][n_tok]
     float *dR;             // [N][n_tok]

@@ -26,6 +26,22 @@ __all__ = ["rstd", "fused_read_supported", "FusedDattnRead", "DattnStack", "_ali
            "FusedCombineStk", "FusedStepStk"]
 
 
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on(dev):
+    """A device guard that costs nothing when `dev` is already the current device (the usual case)."""
+    return _NO_GUARD if dev.index is None or dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+
 def _require_cuda(t: torch.Tensor, what: str) -> None:
     if not t.is_cuda:
         raise RuntimeError(f"loopback_b200.{what}: tensors must live on a CUDA device (there is no CPU path)")
@@ -287,7 +303,8 @@ class DattnStack:
     reads that will see it, DOTS[query, update, token] fp32, and the reads use those; the queries are taken as they
     are when the stack is built, i.e. for one forward pass."""
     __slots__ = ("V", "R", "dV", "dR", "n_steps", "n_tok", "d", "eps", "Q", "QT", "DOTS", "r_done", "_scratch",
-                 "fuse_final", "_scale_done", "_neg", "_last_write", "_dq", "_dh0", "_first_step", "_first_blend")
+                 "fuse_final", "_scale_done", "_neg", "_last_write", "_dq", "_dh0", "_first_step", "_first_blend",
+                 "d_done", "defer_writes", "_pending", "_small")
 
     def __init__(self, n_steps: int, shape, dtype, device, query=None, eps: float = 1e-6):
         b, t, d = shape
@@ -304,7 +321,15 @@ class DattnStack:
         self.R = torch.empty((n_steps, b, t, 1), dtype=torch.float32, device=device)
         self.dV = self.dR = None
         self.eps = float(eps)
-        self.r_done = [False] * self.n_steps      # R[s] (and the scores of update s) written by the write of s
+        self.r_done = [False] * self.n_steps      # R[s] written by the write of s
+        self.d_done = [False] * self.n_steps      # ... and the scores of update s (DOTS[:, s, :])
+        # Decode-sized batches without autograd: with defer_writes a write only records its tensors, and the read that
+        # follows launches ONE kernel for both (lb_step_fwd). The tensor write() returned is filled by that launch,
+        # not before; anything else that touches the stack first (another write, rstd, a read through another entry
+        # point, flush()) performs the recorded write on its own.
+        self.defer_writes = False
+        self._pending = None
+        self._small = b * t <= 4 * torch.cuda.get_device_properties(device).multi_processor_count
         self.Q = self.QT = self.DOTS = None
         self._scratch = None
         # The backward of read s is the last kernel to touch update s, so it also finishes that update's gradient
@@ -326,7 +351,36 @@ class DattnStack:
     def write(self, s: int, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """V[s] = h - x, returned as the update tensor (sharing the stack's storage, with the autograd edge to h
         and x)."""
+        self.flush()
+        if (self.defer_writes and self._small and 1 <= s < self.n_steps and not torch.is_grad_enabled()
+                and h.dtype == self.V.dtype == x.dtype and h.shape == self.V.shape[1:] == x.shape
+                and h.is_contiguous() and x.is_contiguous()):
+            self._pending = (int(s), h, x)
+            return self.V[s]                  # no autograd here: a plain view will do
         return _WriteDelta.apply(self, s, h, x)
+
+    def flush(self) -> None:
+        """Perform a write that was recorded for fusion with its read and has not been launched yet."""
+        if self._pending is not None:
+            s, h, x = self._pending
+            self._pending = None
+            with torch.no_grad():
+                _WriteDelta.apply(self, s, h, x)
+
+    def step_forward(self, step, h, x, h0, beta, tc_prev, lam, c0):
+        """The recorded write of update `step` and the read that follows it as one launch (no autograd): returns
+        (out, tc [n_tok, n])."""
+        n, n_tok, d, dev = step + 1, self.n_tok, self.d, self.V.device
+        self._pending = None
+        out = torch.empty_like(h)
+        tc = torch.empty((n_tok, n), device=dev, dtype=torch.float32)
+        with _on(dev), _timed("step_fwd", n, n + 4 + (h0 is not None)):
+            check(_lib.lib().lb_step_fwd(ptr(h), ptr(x), ptr(h0), float(beta), ptr(self.V), ptr(self.R), ptr(self.Q),
+                                         ptr(tc_prev), float(lam), ptr(c0), ptr(out), ptr(tc), None, None, None, n_tok, d,
+                                         self.n_steps, int(step), self.eps, dtype_code(self.V.dtype), stream_ptr()),
+                  "step forward")
+        self.r_done[step], self.d_done[step] = True, False
+        return out, tc
 
     def rstd(self, s: int, delta: torch.Tensor, eps: float) -> torch.Tensor:
         """R[s] = the key scale of V[s], returned sharing the stack's storage (differentiable through `delta`)."""
@@ -361,7 +415,7 @@ class _WriteDelta(torch.autograd.Function):
             check(_lib.lib().lb_write(ptr(hc), ptr(xc), ptr(stack.V), ptr(stack.R), ptr(stack.Q), ptr(stack.DOTS),
                                       stack.n_tok, stack.d, stack.n_steps, nq, int(s), stack.eps,
                                       dtype_code(stack.V.dtype), stream_ptr()), "write")
-        stack.r_done[s] = True
+        stack.r_done[s], stack.d_done[s] = True, nq > 0
         stack._last_write = (int(s), h, x)
         ctx.stack, ctx.s = stack, int(s)
         return out
@@ -386,6 +440,7 @@ class _WriteDelta(torch.autograd.Function):
 class _RstdStk(torch.autograd.Function):
     @staticmethod
     def forward(ctx, stack: DattnStack, s: int, x: torch.Tensor, eps: float):
+        stack.flush()
         r = _alias(stack.R, s)
         if not (stack.r_done[s] and eps == stack.eps):      # else the write already stored R[s]
             xc = x.detach().contiguous()
@@ -432,7 +487,8 @@ class FusedDattnReadStk(torch.autograd.Function):
         qc = q.detach().float().contiguous()
         c0c = c0.detach().float().contiguous()
         cbar_c = cbar.detach().float().contiguous()
-        if stack.DOTS is not None and step >= 1 and all(stack.r_done[:n]):
+        stack.flush()
+        if stack.DOTS is not None and step >= 1 and all(stack.d_done[:n]):
             dots, qi = stack.DOTS, step - 1           # the stored scores of query step - 1 (q is that query)
         else:
             dots, qi = torch.empty((stack.n_steps, n_tok), device=dev, dtype=torch.float32), 0
@@ -494,7 +550,8 @@ class FusedCombineStk(torch.autograd.Function):
         qc = q.detach().float().contiguous()
         c0c = c0.detach().float().contiguous()
         tcp = tc_prev.detach().float().contiguous()
-        if stack.DOTS is not None and all(stack.r_done[:n]):
+        stack.flush()
+        if stack.DOTS is not None and all(stack.d_done[:n]):
             dots, qi = stack.DOTS, step - 1
         else:
             dots, qi = torch.empty((stack.n_steps, n_tok), device=dev, dtype=torch.float32), 0
@@ -577,7 +634,8 @@ class FusedStepStk(torch.autograd.Function):
             raise RuntimeError("delta_attnres stacked read: the previous read's coefficients must have n - 1 entries")
         c0c = c0.detach().float().contiguous()
         tcp = tc_prev.detach().float().contiguous()
-        if stack.DOTS is not None and all(stack.r_done[:n]):
+        stack.flush()
+        if stack.DOTS is not None and all(stack.d_done[:n]):
             dots, qi, qc = stack.DOTS, step - 1, stack.Q[step - 1]
         else:
             qc = query.detach()[step - 1].float().contiguous()

@@ -4,6 +4,7 @@
     python -m loopback_b200.microbench read_fwd --tokens 32768 --d 1024 --N 24 --n 12 [--blend]
     python -m loopback_b200.microbench read_bwd --tokens 32768 --d 1024 --N 24 --n 12 [--first] [--blend]
     python -m loopback_b200.microbench step_bwd --tokens 32768 --d 1024 --N 24 --n 12 [--first] [--blend]
+    python -m loopback_b200.microbench step_fwd --tokens 64 --d 2048 --N 80 --n 40 --no-flush     (decode-sized)
 
 Prints the average launch time, the row traffic the launch makes by design (GB) and the bandwidth that gives.
 Between launches a buffer larger than L2 is rewritten (--no-flush turns that off), so every launch starts cold like
@@ -21,7 +22,7 @@ from . import _lib as L
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["write", "read_fwd", "read_bwd", "step_bwd"])
+    ap.add_argument("kernel", choices=["write", "read_fwd", "read_bwd", "step_bwd", "step_fwd"])
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--d", type=int, default=1024)
     ap.add_argument("--N", type=int, default=24, help="updates of the pass (N - 1 queries)")
@@ -85,6 +86,14 @@ def main():
         fwd()
         if a.kernel == "read_fwd":
             launch, units, label = fwd, n + 2 + int(a.blend), f"forward read, {n} sources"
+        elif a.kernel == "step_fwd":
+            hh, xx = rnd(T, d), rnd(T, d)
+            units, label = n + 4 + int(a.blend), f"forward step (write + read, one launch), {n} sources"
+
+            def launch():
+                L.check(lib.lb_step_fwd(L.ptr(hh), L.ptr(xx), L.ptr(h0) if a.blend else None, 0.75, L.ptr(V), L.ptr(R),
+                                        L.ptr(Q), L.ptr(tcp), lam, L.ptr(c0), L.ptr(out), L.ptr(tc), None, None, None, T, d,
+                                        N, n - 1, 1e-6, code, st), "step forward")
         else:
             up, gt = rnd(T, d), torch.randn(T, n, device=dev, generator=g)
             dV, dR = rnd(N, T, d), torch.randn(N, T, device=dev, generator=g)

@@ -223,6 +223,63 @@ def test_step_bwd_equals_combine_bwd_plus_the_torch_glue(L, dtype, n_tok, d, n, 
     assert L.device_error() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_tok,d,N,s,blend", [(64, 2048, 80, 79, True), (64, 2048, 80, 40, False), (5, 64, 6, 1, False),
+                                               (37, 768, 12, 5, True), (130, 1024, 24, 23, True), (9, 3072, 8, 3, False),
+                                               (3, 4096, 6, 4, True), (300, 320, 10, 9, False), (17, 136, 130, 127, True)])
+def test_step_fwd_equals_write_then_read(L, dtype, n_tok, d, N, s, blend):
+    """lb_step_fwd (one launch, no cached scores, online softmax) against lb_write followed by lb_combine_fwd: the
+    stored update bit for bit, its key scale, the coefficients and the saved softmax statistics to fp32 round-off,
+    the output to fp32 round-off (fp32 rows) or the last bf16 bit; and the zero-query identity bit for bit."""
+    n, NQ, beta, lam = s + 1, N - 1, 0.75, 0.25 if blend else 1.0
+    g = torch.Generator(device="cuda").manual_seed(n_tok + d + s)
+    code = L.dtype_code(dtype)
+    V = (torch.randn(N, n_tok, d, device="cuda", generator=g) * 0.5).to(dtype)
+    R = torch.rsqrt(V.float().pow(2).mean(-1) + 1e-6).contiguous()
+    h, x, h0 = (torch.randn(n_tok, d, device="cuda", generator=g).to(dtype) for _ in range(3))
+    c0 = (torch.rand(n, device="cuda", generator=g) * 0.9 + 0.1).contiguous()
+    tcp = (c0[:n - 1].view(1, -1) + 0.2 * torch.randn(n_tok, n - 1, device="cuda", generator=g)).contiguous()
+    for zero_query in (False, True):
+        Q = torch.zeros(NQ, d, device="cuda") if zero_query else torch.randn(NQ, d, device="cuda", generator=g) * 0.3
+        tcp_ = (c0[:n - 1] / lam).view(1, -1).expand(n_tok, -1).contiguous() if zero_query else tcp
+        c0_ = (lam * torch.cat((c0[:n - 1] / lam, torch.ones(1, device="cuda")))).contiguous() if zero_query else c0
+        # reference: the two launches, scores cached by the writes
+        V1, R1 = V.clone(), R.clone()
+        DOTS = torch.einsum("ntd,qd->qnt", V1.float(), Q).contiguous()
+        L.check(L.lib().lb_write(L.ptr(h), L.ptr(x), L.ptr(V1), L.ptr(R1), L.ptr(Q), L.ptr(DOTS), n_tok, d, N, NQ, s, 1e-6,
+                                 code, L.stream_ptr()), "write")
+        out1 = torch.empty_like(h)
+        tc1, lg1 = torch.empty(n_tok, n, device="cuda"), torch.empty(n_tok, n, device="cuda")
+        lse1, lse01 = torch.empty(n_tok, device="cuda"), torch.empty(n_tok, device="cuda")
+        L.check(L.lib().lb_combine_fwd(L.ptr(V1), L.ptr(R1), L.ptr(DOTS), s - 1, L.ptr(h), L.ptr(h0) if blend else None,
+                                       beta, L.ptr(tcp_), lam, L.ptr(c0_), L.ptr(out1), L.ptr(tc1), L.ptr(lg1),
+                                       L.ptr(lse1), L.ptr(lse01), n_tok, d, N, n, code, L.stream_ptr()), "combine forward")
+        V2, R2 = V.clone(), R.clone()
+        out2 = torch.full_like(h, float("nan"))
+        tc2, lg2 = torch.full((n_tok, n), float("nan"), device="cuda"), torch.empty(n_tok, n, device="cuda")
+        lse2, lse02 = torch.empty(n_tok, device="cuda"), torch.empty(n_tok, device="cuda")
+        L.check(L.lib().lb_step_fwd(L.ptr(h), L.ptr(x), L.ptr(h0) if blend else None, beta, L.ptr(V2), L.ptr(R2), L.ptr(Q),
+                                    L.ptr(tcp_), lam, L.ptr(c0_), L.ptr(out2), L.ptr(tc2), L.ptr(lg2), L.ptr(lse2),
+                                    L.ptr(lse02), n_tok, d, N, s, 1e-6, code, L.stream_ptr()), "step forward")
+        torch.cuda.synchronize()
+        assert torch.equal(V1, V2), "the stored update must be bit-exact, and no other slice touched"
+        assert rel(R2[s], R1[s]) < 1e-6 and torch.equal(R2[:s], R1[:s])
+        if zero_query:
+            base = h + beta * (h0 - h) if blend else h
+            assert torch.equal(out2, base) and torch.equal(tc2, c0_.view(1, -1).expand(n_tok, -1))
+            continue
+        assert rel(tc2, tc1) < TOL32 and rel(lg2, lg1) < TOL32
+        assert rel(lse2, lse1) < TOL32 and rel(lse02, lse01) < TOL32
+        if dtype == torch.float32:
+            assert rel(out2, out1) < TOL32
+        else:
+            diff = (out2.float() - out1.float()).abs()
+            ulp = out1.float().abs().clamp_min(1e-3) * 2.0 ** -7
+            assert bool((diff <= ulp).all()), "bf16 outputs may differ in the last bit only"
+            assert float((diff > 0).float().mean()) < 0.05
+    assert L.device_error() == 0
+
+
 # ------------------------------------------------------------------------------------------------------------
 # 2. one read, list layout, in the style of the reference's kernel test (tests/test_fused_dattn.py:48-108)
 # ------------------------------------------------------------------------------------------------------------
