@@ -589,6 +589,12 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     const int grid = (int)(p.tok_tiles < cap ? p.tok_tiles : cap);
     cudaError_t e = lb::launch_read_bwd(dtype, fr, ncw, tmV, tmG, tmDV, tmH0, p, grid, st);
     if (e != cudaSuccess) return cuda_fail(e, "lb_read_bwd launch");
+    if (p.dh0 != nullptr && wpt > 1) {
+        // shapes with several warps per token leave the loop input's gradient to a small kernel of its own (in their
+        // main kernel the extra code cost every launch 2-3 %, boundary read or not)
+        e = lb::launch_scale_acc(dtype, g, p.dh0, p.beta, p.dh0_accum, (long long)n_tok * d, di.sms, st);
+        if (e != cudaSuccess) return cuda_fail(e, "lb_step_bwd h0-gradient launch");
+    }
     e = lb::launch_dq_reduce(p.dq_part, grid, dq, d, p.inv_sqrt_d, st);
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_read_bwd dq reduction launch");
 }

@@ -81,6 +81,9 @@ cudaError_t launch_rstd_fwd(int dtype, const void *x, float *r, long long n_tok,
 cudaError_t launch_rstd_bwd(int dtype, const void *x, const float *r, const float *gr, void *gx, long long n_tok,
                             int d, int mode, int sms, cudaStream_t stream);
 cudaError_t launch_neg(int dtype, const void *g, void *out, long long n_elem, int sms, cudaStream_t stream);
+// acc = round(beta g) (accumulate == 0) or round(acc + round(beta g)), storage-type arithmetic
+cudaError_t launch_scale_acc(int dtype, const void *g, void *acc, float beta, int accumulate, long long n_elem, int sms,
+                             cudaStream_t stream);
 
 // One whole forward step for decode-sized batches (lb_step_fwd): one CTA per token, ct column threads x sg source groups
 struct StepSmallParams {

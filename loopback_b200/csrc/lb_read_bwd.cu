@@ -116,7 +116,8 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     __syncthreads();
     const WaitCtx wc{abort_a, p.err_word};
     const long long n_tiles = p.tok_tiles;
-    const bool dh0_rmw = p.dh0 != nullptr && p.dh0_accum != 0;       // the old h0 gradient comes as one more tile
+    // the old h0 gradient comes as one more tile (one-warp-per-token shapes; the others leave h0's gradient to a kernel of its own)
+    const bool dh0_rmw = STEP && SOLO && p.dh0 != nullptr && p.dh0_accum != 0;
     const int items_per_tile = 1 + n + (p.accum ? n : 0) + (dh0_rmw ? 1 : 0);
     // stage layout: token-major [t][chunk][512 B] when one 4-D TMA box fills a stage, chunk-major [chunk][t][512 B]
     // when the row is fetched chunk by chunk
@@ -173,7 +174,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 if (lane == 0) mbar_arrive(empty_a + 8u * st);
                 if (++st == NS) { st = 0; ph ^= 1u; }
             }
-            if (STEP && p.dh0 != nullptr) {
+            if (STEP && SOLO && p.dh0 != nullptr) {
                 // the read closed an iteration (base = h + beta (h0 - h)): h0's share of g, round(beta g), leaves at
                 // once -- written, or added to what earlier backward reads of the pass left there (that tile is the
                 // next item of the ring)
@@ -326,17 +327,15 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 }
             }
             if constexpr (STEP) {
-                T *const dvrow0 = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d + chunk0 * BW + lane * VEC;
+                T *dvrow = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d + chunk0 * BW + lane * VEC;
                 const long long src_stride = p.n_tok * (long long)p.d;
-                // One source of phase 2. FINAL (compile time) is the newest source of a finalising read. It goes FIRST:
-                // the fragments of that source kept from phase 1 (for its key-scale term) are then dead for the loop
-                // over the older sources, and the loop body carries none of the extra outputs.
+                // One source of phase 2. FINAL (compile time) is the newest source of a finalising read, peeled out of the
+                // loop over the older sources so that the loop body carries none of its extra outputs.
                 auto phase2_source = [&](int i, auto final_tag) {
                     constexpr bool FINAL = decltype(final_tag)::value;
                     const uint32_t i4 = (uint32_t)i * BT4;
                     const float wi = lds_f32(tb + 3u * tfl4 + i4), kq = lds_f32(gk + i4);
                     const float2 w2 = make_float2(wi, wi), kq2 = make_float2(kq, kq);
-                    T *const dvrow = dvrow0 + i * src_stride;
                     uint4 prev[FR];
                     if (p.accum) {
                         if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
@@ -391,9 +390,14 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                             if (live) st_global_v4(dvrow + k * BW, res);
                         }
                     }
+                    if constexpr (!FINAL) dvrow += src_stride;
                 };
-                phase2_source(n - 1, std::true_type{});
+                // One warp per token: the finished source first, which frees the registers that hold its fragments for
+                // the loop over the older ones. Several warps per token: last, as in the plain kernel (measured: the
+                // other order costs those shapes 3 %, and this one costs the one-warp shape 6 %).
+                if constexpr (SOLO) phase2_source(n - 1, std::true_type{});
                 for (int i = 0; i < n - 1; ++i) phase2_source(i, std::false_type{});
+                if constexpr (!SOLO) phase2_source(n - 1, std::true_type{});
             } else {
                 T *dvrow = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d + chunk0 * BW + lane * VEC;
                 const long long src_stride = p.n_tok * (long long)p.d;
@@ -470,7 +474,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             if (dh0_rmw) tma_prefetch_desc(&tmH0);
             const int v0 = dh0_rmw ? 2 : 1;                      // first V item; item 1 is the h0-gradient tile if any
             // the order in which phase 2 wants the old gradients: a finalising read takes the newest source first
-            auto dv_source = [&](int j) { return STEP ? (j == 0 ? n - 1 : j - 1) : j; };
+            auto dv_source = [&](int j) { return STEP && SOLO ? (j == 0 ? n - 1 : j - 1) : j; };
             int st = 0; uint32_t ph = 0;
             int issued = 0;
             bool ok = true;

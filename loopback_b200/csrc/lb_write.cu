@@ -374,6 +374,25 @@ __global__ void __launch_bounds__(256) neg_kernel(const T *__restrict__ g, T *__
     }
 }
 
+// acc = round(beta g), or acc = round(acc + round(beta g)): the boundary blend's gradient of the loop input, in the
+// storage type's arithmetic (what autograd's mul and in-place accumulation give).
+template <typename T>
+__global__ void __launch_bounds__(256) scale_acc_kernel(const T *__restrict__ g, T *__restrict__ acc, float beta, int accumulate,
+                                                        long long n_frag) {
+    using S = Store<T>;
+    constexpr int P = S::kPairs;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const float2 b2 = make_float2(beta, beta);
+    for (long long f = (long long)blockIdx.x * blockDim.x + threadIdx.x; f < n_frag; f += stride) {
+        float2 v[P];
+        S::unpack2(ld_global_stream_v4(g + f * S::kVec), v);
+#pragma unroll
+        for (int e = 0; e < P; ++e) v[e] = __fmul2_rn(b2, v[e]);
+        const uint4 r = accumulate ? S::accum(*reinterpret_cast<const uint4 *>(acc + f * S::kVec), v) : S::pack2v(v);
+        st_global_v4(acc + f * S::kVec, r);
+    }
+}
+
 static int grid_for(long long work_items, int per_block, int sms, int waves) {
     long long blocks = (work_items + per_block - 1) / per_block;
     const long long cap = (long long)sms * waves;
@@ -415,6 +434,21 @@ cudaError_t launch_neg(int dtype, const void *g, void *out, long long n_elem, in
                                                             static_cast<__nv_bfloat16 *>(out), n_frag);
     else
         neg_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float *>(g), static_cast<float *>(out), n_frag);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scale_acc(int dtype, const void *g, void *acc, float beta, int accumulate, long long n_elem, int sms,
+                             cudaStream_t stream) {
+    if (n_elem == 0) return cudaSuccess;
+    const int vec = dtype == LB_DTYPE_BF16 ? 8 : 4;
+    const long long n_frag = n_elem / vec;
+    const int grid = grid_for(n_frag, 256, sms, 16);
+    if (dtype == LB_DTYPE_BF16)
+        scale_acc_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(g),
+                                                                  static_cast<__nv_bfloat16 *>(acc), beta, accumulate, n_frag);
+    else
+        scale_acc_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float *>(g), static_cast<float *>(acc), beta,
+                                                          accumulate, n_frag);
     return cudaGetLastError();
 }
 
