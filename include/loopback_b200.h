@@ -62,7 +62,10 @@ int lb_device_error(int clear);
  * tiled write kernel, whatever the batch size; 3: the tensor-core write kernel whatever the batch size),
  * "write_mt" (16-token tiles per consumer warp of the tensor-core write kernel: 1 or 2),
  * "write_tile" (tokens per tile of the tensor-core write kernel: a multiple of 32 up to 256), "write_stages" (its TMA
- * ring depth, 2..8), "fwd_sps" (sources per TMA stage of the forward read: 1, 2 or 4). Value 0 restores the default
+ * ring depth, 2..8), "fwd_sps" (sources per TMA stage of the forward read: 1, 2 or 4), "wait_cycles" (the limit of
+ * every bounded wait inside the kernels, in GPU clock cycles; default 4e9), "test_skip_item" (test hook: the first
+ * CTA of the next forward reads leaves out its k-th tile copy, so that a bounded wait runs out, the CTA unwinds and
+ * lb_device_error reports it; nothing traps or hangs). Value 0 restores the default
  * (chosen by size); the name "reset_all" restores every knob. Returns LB_ERR_ARG for an unknown name.
  * The knobs are one process-wide table without a lock: set them from one thread, while no other thread is inside
  * a call of this library. */

@@ -37,7 +37,7 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 struct Options {
     int fwd_stages = 0, bwd_stages = 0, fwd_fr = 0, grid_cap = 0, fwd_warps = 0, bwd_warps = 0, bwd_wpt = 0,
-        tma_per_chunk = 0, write_tt = 0, write_mt = 0, fwd_sps = 0, write_tile = 0, write_stages = 0;
+        tma_per_chunk = 0, write_tt = 0, write_mt = 0, fwd_sps = 0, write_tile = 0, write_stages = 0, wait_cycles = 0, test_skip_item = 0;
 } g_opt;
 
 struct DeviceInfo {
@@ -141,6 +141,8 @@ int make_map_sw128(CUtensorMap *m, const void *base, long long n_tok, int d, int
     return LB_OK;
 }
 
+long long wait_limit() { return g_opt.wait_cycles > 0 ? (long long)g_opt.wait_cycles : lb::kWaitCycles; }
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_common(long long n_tok, int d, int dtype) {
@@ -201,6 +203,8 @@ int lb_set_option(const char *name, int value) {
     else if (!strcmp(name, "fwd_sps")) g_opt.fwd_sps = value;
     else if (!strcmp(name, "write_tile")) g_opt.write_tile = value;
     else if (!strcmp(name, "write_stages")) g_opt.write_stages = value;
+    else if (!strcmp(name, "wait_cycles")) g_opt.wait_cycles = value;
+    else if (!strcmp(name, "test_skip_item")) g_opt.test_skip_item = value;
     else return fail(LB_ERR_ARG, "unknown option '%s'", name);
     return LB_OK;
 }
@@ -243,6 +247,7 @@ int lb_write(const void *h, const void *x, void *V, float *R, const float *Q, fl
         mp.chunks = (d + 63) / 64;
         mp.n_tiles = (n_tok + mp.tile_tok - 1) / mp.tile_tok;
         mp.err_word = di.err_word;
+        mp.wait_cycles = wait_limit();
         mp.stages = g_opt.write_stages >= 2 && g_opt.write_stages <= 8 ? g_opt.write_stages : 4;
         while (mp.stages > 2 && lb::write_mma_smem_bytes(nt, mp.tile_tok, mp.stages) > 227 * 1024) --mp.stages;
         CUtensorMap tmH, tmX;
@@ -413,6 +418,7 @@ static int read_fwd_impl(const void *V, const float *R, const float *DOTS, int q
     p.rank4 = rank4 ? 1 : 0;
     p.inv_sqrt_d = 1.0f / sqrtf((float)d);
     p.err_word = di.err_word;
+    p.wait_cycles = wait_limit(); p.test_skip_item = g_opt.test_skip_item;
     const long long tiles = tok_tiles * cg;
     int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
     if (cap > kMaxGrid) cap = kMaxGrid;
@@ -583,7 +589,7 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     p.neg_out = finalize ? neg_out : nullptr; p.inv_sqrt_d = 1.0f / sqrtf((float)d);
     p.dh_out = finalize ? sg.dh : nullptr; p.dh0 = finalize ? sg.dh0 : nullptr; p.dh0_accum = sg.dh0_accum;
     p.blend = sg.blend; p.beta = sg.beta; p.skip_final_store = finalize ? sg.skip_final_store : 0;
-    p.err_word = di.err_word;
+    p.err_word = di.err_word; p.wait_cycles = wait_limit();
     int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
     if (cap > kMaxGrid) cap = kMaxGrid;
     const int grid = (int)(p.tok_tiles < cap ? p.tok_tiles : cap);

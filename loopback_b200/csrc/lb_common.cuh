@@ -103,11 +103,12 @@ __device__ __forceinline__ void sts_f4(uint32_t a, const float4 &v) {
 
 // Bounded wait. The abort flag lives in shared memory: the first wait of a CTA that runs out sets it (and the
 // device error word), every later wait of that CTA then fails at once, so a stuck CTA unwinds in one time-out.
-constexpr long long kWaitCycles = 4000000000LL;   // ~2 s at B200 clocks
+constexpr long long kWaitCycles = 4000000000LL;   // the default limit: ~2 s at B200 clocks
 
 struct WaitCtx {
     uint32_t abort_flag;        // shared-window address of the CTA's abort flag
     int *err_word;              // global memory, per device
+    long long limit;            // cycles a wait may take (kWaitCycles unless the "wait_cycles" option says otherwise)
 };
 
 // `relaxed` waits (the scalar warps': they run a tile ahead of the consumers) sleep between polls, so
@@ -121,7 +122,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
         if (kRelaxed) __nanosleep(128);
         if ((++spins & 255u) == 0u) {
             if (lds_volatile_s32(wc.abort_flag)) return false;
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > wc.limit) {
                 sts_s32(wc.abort_flag, what);
                 atomicCAS(wc.err_word, 0, what);
                 return false;

@@ -37,6 +37,9 @@ struct ReadFwdParams {
     int sps;               // sources per stage (1..4; > 1 only with rank4)
     float inv_sqrt_d;
     int *err_word;         // device error word (see lb_device_error)
+    long long wait_cycles; // limit of every bounded wait
+    int test_skip_item;    // test hook: CTA 0's producer leaves out its k-th tile copy (0 = off), so that a consumer's
+                           // bounded wait runs out and the unwinding path executes
 };
 
 size_t read_fwd_smem_bytes(int fr, int ncw, int stages, int sps);
@@ -70,6 +73,7 @@ struct WriteMmaParams : WriteParams {
     int stages;            // TMA ring depth (2..4)
     long long n_tiles;
     int *err_word;
+    long long wait_cycles;
 };
 int write_mma_ntiles(int nq);                                   // query tiles of 8 the kernel is built for, or -1
 size_t write_mma_smem_bytes(int nt, int tile_tok, int stages);
@@ -137,6 +141,7 @@ struct ReadBwdParams {
     int blend;             // 1: the read closed an iteration (base = h + beta (h0 - h))
     float beta;
     int skip_final_store;  // 1: dV[n-1] itself is not stored (nothing reads it after its last reader)
+    long long wait_cycles; // limit of every bounded wait
     float inv_sqrt_d;
     int *err_word;
 };

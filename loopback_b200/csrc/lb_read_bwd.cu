@@ -114,7 +114,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                                                   : make_float4(0.f, 0.f, 0.f, 0.f));
     }
     __syncthreads();
-    const WaitCtx wc{abort_a, p.err_word};
+    const WaitCtx wc{abort_a, p.err_word, p.wait_cycles};
     const long long n_tiles = p.tok_tiles;
     // the old h0 gradient comes as one more tile (one-warp-per-token shapes; the others leave h0's gradient to a kernel of its own)
     const bool dh0_rmw = STEP && SOLO && p.dh0 != nullptr && p.dh0_accum != 0;
@@ -506,15 +506,16 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     if (++st == NS) { st = 0; ph ^= 1u; }
                 }
             }
-            if (!ok) {
-                // unwinding: let the copies already issued land before the CTA's shared memory is released --
+            if (!ok || lds_volatile_s32(abort_a) != 0) {
+                // unwinding (this lane's own wait ran out, or a consumer's did and the consumers stopped waiting for
+                // their tiles): let the copies already issued land before the CTA's shared memory is released --
                 // the last min(issued, NS) fills, walking the ring backwards from the current position
                 long long t0 = clock64();
                 int ds = st; uint32_t dp = ph;
                 for (int k = 0; k < NS && k < issued; ++k) {
                     if (--ds < 0) { ds = NS - 1; dp ^= 1u; }
                     while (!mbar_try_wait(full_a + 8u * ds, dp)) {
-                        if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
+                        if (clock64() - t0 > p.wait_cycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
                     }
                 }
             }

@@ -91,7 +91,7 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         if (lane == 0) sts_f32(mass_a, m);
     }
     __syncthreads();
-    const WaitCtx wc{abort_a, p.err_word};
+    const WaitCtx wc{abort_a, p.err_word, p.wait_cycles};
 
     const int cg_count = p.col_groups;
     const long long n_tiles = (long long)p.tok_tiles * cg_count;
@@ -225,6 +225,12 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                         break;
                     }
                     const uint32_t sb = stages_a + (uint32_t)st * kPitch, fb = full_a + 8u * st;
+                    if (p.test_skip_item != 0 && blockIdx.x == 0 && issued + 1 == p.test_skip_item) {
+                        // test hook: this copy is left out, so its consumers' bounded wait runs out and the CTA unwinds
+                        ++issued;
+                        if (++st == NS) { st = 0; ph ^= 1u; }
+                        continue;
+                    }
                     if (p.rank4) {          // one box: CPT chunks x BT tokens (x SPS sources); what lies past the row or
                                             // the stack is zero-filled and counts toward the bytes all the same
                         mbar_arrive_expect_tx(fb, item < 0 ? kStageBytes : kPitch);
@@ -242,15 +248,16 @@ read_fwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     if (++st == NS) { st = 0; ph ^= 1u; }
                 }
             }
-            if (!ok) {
-                // unwinding: let the copies already issued land before the CTA's shared memory is released --
+            if (!ok || lds_volatile_s32(abort_a) != 0) {
+                // unwinding (this lane's own wait ran out, or a consumer's did and the consumers stopped waiting for
+                // their tiles): let the copies already issued land before the CTA's shared memory is released --
                 // the last min(issued, NS) fills, walking the ring backwards from the current position
                 long long t0 = clock64();
                 int ds = st; uint32_t dp = ph;
                 for (int k = 0; k < NS && k < issued; ++k) {
                     if (--ds < 0) { ds = NS - 1; dp ^= 1u; }
                     while (!mbar_try_wait(full_a + 8u * ds, dp)) {
-                        if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
+                        if (clock64() - t0 > p.wait_cycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
                     }
                 }
             }

@@ -94,7 +94,7 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
         fence_mbar_init();
     }
     __syncthreads();
-    const WaitCtx wc{abort_a, p.err_word};
+    const WaitCtx wc{abort_a, p.err_word, p.wait_cycles};
     const int chunks = p.chunks;
     const int nq = NT > 0 ? p.nq : 0;
 
@@ -277,14 +277,15 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                     if (++st == NS) { st = 0; ph ^= 1u; }
                 }
             }
-            if (!ok) {
-                // unwinding: let the copies already issued land before the CTA's shared memory is released
+            if (!ok || lds_volatile_s32(abort_a) != 0) {
+                // unwinding (this lane's own wait ran out, or a consumer's did and the consumers stopped waiting for
+                // their tiles): let the copies already issued land before the CTA's shared memory is released
                 long long t0 = clock64();
                 int ds = st; uint32_t dp = ph;
                 for (int k = 0; k < NS && k < issued; ++k) {
                     if (--ds < 0) { ds = NS - 1; dp ^= 1u; }
                     while (!mbar_try_wait(full_a + 8u * ds, dp)) {
-                        if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
+                        if (clock64() - t0 > p.wait_cycles) { atomicCAS(p.err_word, 0, kDevWaitDrain); break; }
                     }
                 }
             }

@@ -23,23 +23,31 @@ def shard_tokens(n_tok: int, rank: int, world: int) -> tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
-def allreduce_query_grad(grad: torch.Tensor, group=None, expected_shape=None) -> torch.Tensor:
+def allreduce_query_grad(grad: torch.Tensor, group=None, expected_shape=None, check: bool = True) -> torch.Tensor:
     """Sum the local query gradient over the ranks of `group`, in fp32, in place when `grad` is fp32.
 
-    Every rank must pass the same shape; a mismatch is detected on the host before the collective (each rank
-    contributes its shape to a small all-gather) and raises on every rank instead of hanging or corrupting."""
+    Every rank must pass the same shape. With `check` (the default) each rank contributes its shape, and whether it
+    matches `expected_shape`, to a small all-gather first, and EVERY rank raises after that exchange if any of them
+    disagrees -- none is left waiting in a collective its peer never joins. The exchange costs a host synchronisation
+    per call; a training loop checks on its first pass and calls with check=False afterwards, which issues the
+    all-reduce only."""
     if not dist.is_available() or not dist.is_initialized():
         return grad
     world = dist.get_world_size(group)
     if world == 1:
         return grad
-    if expected_shape is not None and tuple(grad.shape) != tuple(expected_shape):
-        raise ValueError(f"query gradient has shape {tuple(grad.shape)}, expected {tuple(expected_shape)}")
-    shape = torch.tensor(list(grad.shape) + [0] * (4 - grad.dim()), dtype=torch.int64, device=grad.device)
-    shapes = [torch.empty_like(shape) for _ in range(world)]
-    dist.all_gather(shapes, shape, group=group)
-    if any(not torch.equal(s, shape) for s in shapes):
-        raise RuntimeError("query gradient shapes differ across ranks: " + str([s.tolist() for s in shapes]))
+    if check:
+        ok = expected_shape is None or tuple(grad.shape) == tuple(expected_shape)
+        rec = torch.tensor(list(grad.shape) + [0] * (4 - grad.dim()) + [1 if ok else 0], dtype=torch.int64,
+                           device=grad.device)
+        recs = [torch.empty_like(rec) for _ in range(world)]
+        dist.all_gather(recs, rec, group=group)
+        bad = [r for r, x in enumerate(recs) if int(x[4]) == 0]
+        if bad:
+            raise ValueError(f"query gradient shape differs from the expected {tuple(expected_shape)} on ranks {bad}: "
+                             + str([x[:4].tolist() for x in recs]))
+        if any(not torch.equal(x[:4], rec[:4]) for x in recs):
+            raise RuntimeError("query gradient shapes differ across ranks: " + str([x[:4].tolist() for x in recs]))
     if grad.dtype == torch.float32:
         dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=group)
         return grad

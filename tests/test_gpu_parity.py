@@ -791,6 +791,43 @@ def test_error_behaviour(FD):
     assert not FD.fused_read_supported(x.cpu(), [x.cpu()], [torch.ones(1, 4, 1)], torch.ones(1, 4, 1))
 
 
+def test_a_wait_that_runs_out_unwinds_and_reports(L):
+    """The kernels' waits are bounded. With the limit set to about a millisecond and the test hook that makes the first
+    CTA's producer leave out one tile copy, that CTA's consumers give up their wait: the kernel RETURNS (nothing traps,
+    nothing spins on), the device error word names the wait, the other CTAs' tokens are written as usual, and the
+    next launch is unaffected."""
+    n_tok, d, N, n = 2000, 1024, 8, 6
+    g = torch.Generator(device="cuda").manual_seed(5)
+    V = (torch.randn(N, n_tok, d, device="cuda", generator=g) * 0.5).bfloat16()
+    R = torch.rsqrt(V.float().pow(2).mean(-1) + 1e-6).contiguous()
+    dots = torch.randn(N, n_tok, device="cuda", generator=g)
+    base = torch.randn(n_tok, d, device="cuda", generator=g).bfloat16()
+    c0 = (torch.rand(n, device="cuda", generator=g) * 0.9 + 0.1).contiguous()
+    cbar = (c0.view(1, -1) + 0.2 * torch.randn(n_tok, n, device="cuda", generator=g)).contiguous()
+
+    def run():
+        out = torch.full_like(base, float("nan"))
+        tc = torch.empty(n_tok, n, device="cuda")
+        L.check(L.lib().lb_read_fwd(L.ptr(V), L.ptr(R), L.ptr(dots), 0, L.ptr(base), L.ptr(cbar), L.ptr(c0), L.ptr(out),
+                                    L.ptr(tc), None, None, None, n_tok, d, N, n, L.LB_DTYPE_BF16, L.stream_ptr()), "fwd")
+        torch.cuda.synchronize()
+        return out
+
+    good = run()
+    assert L.device_error() == 0 and torch.isfinite(good.float()).all()
+    L.set_option("wait_cycles", 2_000_000)
+    L.set_option("test_skip_item", 3)
+    try:
+        bad = run()
+    finally:
+        L.reset_options()
+    assert L.device_error(clear=True) == 1, "the consumers' wait for a tile (code 1) must be on record"
+    assert torch.equal(bad[8:1184], good[8:1184]), "tokens of the other CTAs are written as usual"
+    assert torch.isnan(bad[:8].float()).any(), "the CTA that gave up stores nothing for the tile it could not finish"
+    again = run()
+    assert L.device_error() == 0 and torch.equal(again, good)
+
+
 # ------------------------------------------------------------------------------------------------------------
 # 6. full-size properties (benchmark configuration 2 shapes: 32768 tokens, d=1024, bf16, N=24)
 # ------------------------------------------------------------------------------------------------------------

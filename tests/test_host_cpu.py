@@ -114,6 +114,19 @@ elif mode == "mismatch":
         assert "differ" in str(e)
     else:
         raise SystemExit("a shape mismatch across ranks went undetected")
+elif mode == "expected":
+    # one rank holds a gradient of the wrong shape: BOTH ranks raise, after the exchange, and neither is left waiting
+    g = torch.zeros(3, 8) if rank == 0 else torch.zeros(4, 8)
+    try:
+        allreduce_query_grad(g, expected_shape=(3, 8))
+    except ValueError as e:
+        assert "ranks [1]" in str(e), str(e)
+    else:
+        raise SystemExit("a wrong shape on a peer went undetected")
+    # check=False: the all-reduce alone
+    g2 = torch.full((3, 8), float(rank + 1))
+    allreduce_query_grad(g2, check=False)
+    assert float(g2[0, 0]) == 3.0
 elif mode == "raise":
     # a rank that fails before the exchange: the survivor's collective ends with an error instead of hanging
     if rank == 1:
@@ -149,6 +162,10 @@ def test_query_grad_allreduce_two_gloo_ranks():
 
 def test_shape_mismatch_is_detected_on_every_rank():
     _spawn("mismatch")
+
+
+def test_unexpected_shape_on_one_rank_raises_on_all():
+    _spawn("expected")
 
 
 def test_rank_failure_does_not_hang_the_survivor():
