@@ -89,6 +89,19 @@ __global__ void __launch_bounds__(MAXT, 1) step_small_kernel(StepSmallParams p) 
         const float4 q4 = col_ok ? __ldg(reinterpret_cast<const float4 *>(p.q + col) + e4) : make_float4(0.f, 0.f, 0.f, 0.f);
         q2[2 * e4] = make_float2(q4.x, q4.y); q2[2 * e4 + 1] = make_float2(q4.z, q4.w);
     }
+    // the first warp will run the token's softmaxes: it requests the scalars it needs now, so that their latency
+    // passes under the first sweep
+    constexpr int NPL = kMaxSources / 32;
+    float pre_r[NPL], pre_c0[NPL], pre_cb[NPL];
+    if (threadIdx.x < 32) {
+#pragma unroll
+        for (int k = 0; k < NPL; ++k) {
+            const int i = lane + 32 * k;
+            pre_r[k] = i < s ? __ldg(p.R + (long long)i * p.n_tok + t) : 0.f;
+            pre_c0[k] = i < n ? __ldg(p.c0 + i) : 0.f;
+            pre_cb[k] = i < n - 1 ? p.lam * __ldg(p.tc_prev + t * (n - 1) + i) : p.lam;
+        }
+    }
     auto dot_of = [&](const uint4 &u) {
         float2 v[P];
         S::unpack2(u, v);
@@ -153,7 +166,6 @@ __global__ void __launch_bounds__(MAXT, 1) step_small_kernel(StepSmallParams p) 
     // ---- the n scalars of the token, by the first warp (lanes over sources, four sources per lane): both softmaxes
     // through the same instructions, so a zero query gives tc == c0 exactly and coefficient deltas of exactly zero
     if (threadIdx.x < 32) {
-        constexpr int NPL = kMaxSources / 32;
         float ssq = 0.f;
         for (int w = 0; w < WPG; ++w) ssq += sm.ssq[w];
         const float rnew = rsqrtf(ssq / (float)p.d + p.eps);
@@ -166,8 +178,8 @@ __global__ void __launch_bounds__(MAXT, 1) step_small_kernel(StepSmallParams p) 
             if (i < n) {
                 float dsum = 0.f;
                 for (int w = 0; w < WPG; ++w) dsum += sm.part[w][i];
-                const float r = i < s ? __ldg(p.R + (long long)i * p.n_tok + t) : rnew;
-                c0v[k] = __ldg(p.c0 + i);
+                const float r = i < s ? pre_r[k] : rnew;
+                c0v[k] = pre_c0[k];
                 lcv[k] = logf(fmaxf(c0v[k], 1e-8f));
                 l[k] = dsum * r * p.inv_sqrt_d + lcv[k];
             }
@@ -192,8 +204,7 @@ __global__ void __launch_bounds__(MAXT, 1) step_small_kernel(StepSmallParams p) 
             const int i = lane + 32 * k;
             if (i < n) {
                 const float tc = c0v[k] + mass * (expf(l[k] - lse) - expf(lcv[k] - lse0));
-                const float cb = i < n - 1 ? p.lam * __ldg(p.tc_prev + t * (n - 1) + i) : p.lam;
-                sm.w[i] = tc - cb;
+                sm.w[i] = tc - pre_cb[k];
                 p.TC[t * n + i] = tc;
                 if (p.LG) p.LG[t * n + i] = l[k];
             }
