@@ -190,6 +190,25 @@ int lb_step_bwd(const void *V, const float *R, void *dV, float *dR, const float 
                 float *dtc_prev, float *dq, void *scratch, void *dh, void *dx, void *dh0, int dh0_accum, int blend,
                 float beta, int64_t n_tok, int d, int N, int n, int accum, int dtype, void *stream);
 
+/* lb_step_bwd without a gradient stack. The plain forms add every read's contribution into dV[i] as the reads'
+ * backwards run (each source row read and written once per later read: N^2 row transfers per pass). This form defers:
+ * the backward of step s = n - 1 keeps its upstream gradient (G[s] = g, a stack like V) and, per older source i and
+ * token, the two scalars of its contribution (Wt[s][i], KQt[s][i]: the coefficients of g and of the step's query), and
+ * forms the finished gradient of ITS OWN update in one go from what the backward steps before it left:
+ *   dV_s = sum over s' >= s of (Wt[s'][s] G[s'] + KQt[s'][s] Q[s'-1]) + the key-scale term,   fp32, rounded once
+ * (N^2 / 2 row reads, no gradient row written except the outputs). Outputs, blend and dh0 exactly as lb_step_bwd; dR is
+ * still accumulated in place (first != 0: written). The step-1 backward (n == 2) also finishes update 0, which has no
+ * step of its own: dv0 receives its gradient (key-scale term included), dx0 the negation; NULL otherwise.
+ * G [N][n_tok][d] storage dtype; Wt, KQt [N][N][n_tok] fp32; Q [N-1][d] fp32 (every query; this step's is row n - 2).
+ * Every backward step of a pass must use this form, last step first, for the sums to be complete.
+ * More accurate than the in-place accumulation it replaces (autograd's, fused_dattn.py:528-531, rounds after every
+ * add); same reference code replaced as lb_step_bwd. */
+int lb_step_bwd_deferred(const void *V, const float *R, void *G, float *dR, float *Wt, float *KQt, const float *Q,
+                         const void *g, const float *gt, const float *tc_prev, float lam, const float *c0, const float *LG,
+                         const float *LSE, const float *LSE0, float *dtc_prev, float *dq, void *scratch, void *dh, void *dx,
+                         void *dh0, int dh0_accum, int blend, float beta, void *dv0, void *dx0, int64_t n_tok, int d, int N,
+                         int n, int first, int dtype, void *stream);
+
 /* The widest row lb_read_bwd_noalloc accepts. */
 #define LB_NOALLOC_MAX_D 3072
 

@@ -44,6 +44,8 @@ SYMBOLS = {
                             _i, _i, _i, _i, _i, _vp]),
     "lb_step_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                          _f, _i64, _i, _i, _i, _i, _i, _vp]),
+    "lb_step_bwd_deferred": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                  _vp, _vp, _i, _i, _f, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp]),
     "lb_read_bwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
                                  _i, _i, _vp]),
 }
@@ -89,7 +91,8 @@ def stream_ptr(device=None):
 # kernels launched through this binding since import (lb_read_bwd launches two: the backward and the reduction
 # of its query-gradient partials); read by the benchmark
 LAUNCHES = {"count": 0}
-_KERNELS_PER_CALL = {"read backward": 2, "read backward (final)": 2, "combine backward": 2, "step backward": 2}
+_KERNELS_PER_CALL = {"read backward": 2, "read backward (final)": 2, "combine backward": 2, "step backward": 2,
+                     "step backward (deferred)": 2}
 
 
 def check(rc: int, what: str) -> None:

@@ -33,6 +33,7 @@ class LoopDeltaAttnRes(nn.Module):
         self.query = nn.Parameter(torch.zeros(self.num_steps - 1, self.dim))
         self.fuse_prologue = True      # fold the boundary blend and the coefficient append/decay into the kernels
         self.fuse_step = True          # ... and make the write and the read of a step one autograd node
+        self.deferred_grads = True     # ... whose backward keeps no gradient stack (DattnStack.deferred_grads)
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -76,6 +77,7 @@ class LoopDeltaAttnRes(nn.Module):
         stack = FD.DattnStack(self.num_steps, tuple(shape), dtype, device, query=self.query if scores else None,
                               eps=self.eps)
         stack.defer_writes = bool(fuse_decode and scores)
+        stack.deferred_grads = bool(self.deferred_grads)
         return stack
 
     def combine(self, proposal, h0, deltas, coeffs, prior_coeffs, loop_idx, block_idx, keys=None, stack=None):

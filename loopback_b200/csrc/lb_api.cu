@@ -468,6 +468,11 @@ struct StepGrads {
     int blend = 0;
     float beta = 0.f;
     int skip_final_store = 0;
+    // the deferred form (G != null): no gradient stack; `dV` of read_bwd_impl is then the g stack
+    float *Wt = nullptr, *KQt = nullptr;
+    const float *Qall = nullptr;
+    int deferred = 0;
+    void *dv0 = nullptr, *dx0 = nullptr;
 };
 
 static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
@@ -518,6 +523,28 @@ int lb_step_bwd(const void *V, const float *R, void *dV, float *dR, const float 
     sg.skip_final_store = 1;
     return read_bwd_impl(V, R, dV, dR, q, g, gt, nullptr, tc_prev, lam, c0, LG, LSE, LSE0, dtc_prev, dq, scratch, n_tok, d,
                          N, n, accum, 1, dx, dtype, stream, sg);
+}
+
+int lb_step_bwd_deferred(const void *V, const float *R, void *G, float *dR, float *Wt, float *KQt, const float *Q,
+                         const void *g, const float *gt, const float *tc_prev, float lam, const float *c0, const float *LG,
+                         const float *LSE, const float *LSE0, float *dtc_prev, float *dq, void *scratch, void *dh, void *dx,
+                         void *dh0, int dh0_accum, int blend, float beta, void *dv0, void *dx0, int64_t n_tok, int d, int N,
+                         int n, int first, int dtype, void *stream) {
+    if (n < 2 || !tc_prev) return fail(LB_ERR_ARG, "lb_step_bwd_deferred: needs n >= 2 and the previous read's coefficients");
+    if (!G || !Wt || !KQt || !Q || !dh || !dx) return fail(LB_ERR_ARG, "lb_step_bwd_deferred: NULL pointer");
+    if (!aligned16(G) || !aligned16(Q) || !aligned16(dh) || !aligned16(dx) || (dh0 && !aligned16(dh0)) ||
+        (dv0 && !aligned16(dv0)) || (dx0 && !aligned16(dx0)))
+        return fail(LB_ERR_ALIGN, "lb_step_bwd_deferred: G, Q, dh, dx, dh0, dv0 and dx0 must be 16-byte aligned");
+    if (((long long)d * 4) % 16) return fail(LB_ERR_ALIGN, "lb_step_bwd_deferred: the query rows must be multiples of 16 bytes");
+    if (dh0 && !blend) return fail(LB_ERR_ARG, "lb_step_bwd_deferred: dh0 is only produced by a read that closes an iteration");
+    if ((dv0 != nullptr) != (dx0 != nullptr) || (dv0 && n != 2))
+        return fail(LB_ERR_ARG, "lb_step_bwd_deferred: dv0 and dx0 come together, from the step-1 backward (n == 2) only");
+    StepGrads sg;
+    sg.dh = dh; sg.dh0 = dh0; sg.dh0_accum = dh0 ? dh0_accum : 0; sg.blend = blend ? 1 : 0; sg.beta = beta;
+    sg.skip_final_store = 1;
+    sg.deferred = 1; sg.Wt = Wt; sg.KQt = KQt; sg.Qall = Q; sg.dv0 = dv0; sg.dx0 = dx0;
+    return read_bwd_impl(V, R, G, dR, Q + (long long)(n - 2) * d, g, gt, nullptr, tc_prev, lam, c0, LG, LSE, LSE0, dtc_prev, dq,
+                         scratch, n_tok, d, N, n, first ? 0 : 1, 1, dx, dtype, stream, sg);
 }
 
 static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, const float *q, const void *g,
@@ -571,8 +598,9 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     const int vec = dtype == LB_DTYPE_BF16 ? 8 : 4;
     int stages = g_opt.bwd_stages > 0 ? g_opt.bwd_stages : 8;
     if (stages > 12) stages = 12;
-    while (stages > 2 && lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec) > kMaxSmem) --stages;
-    if (lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec) > kMaxSmem)
+    const int earlier = sg.deferred ? N - n : 0, qrow = sg.deferred ? d * 4 : 0;
+    while (stages > 2 && lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec, earlier, qrow) > kMaxSmem) --stages;
+    if (lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec, earlier, qrow) > kMaxSmem)
         return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: shared memory does not fit for d=%d, n=%d", d, n);
 
     CUtensorMap tmV, tmG, tmDV, tmH0;
@@ -590,6 +618,10 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     p.dh_out = finalize ? sg.dh : nullptr; p.dh0 = finalize ? sg.dh0 : nullptr; p.dh0_accum = sg.dh0_accum;
     p.blend = sg.blend; p.beta = sg.beta; p.skip_final_store = finalize ? sg.skip_final_store : 0;
     p.err_word = di.err_word; p.wait_cycles = wait_limit();
+    if (sg.deferred) {
+        p.Gst = dV; p.Wt = sg.Wt; p.KQt = sg.KQt; p.Qall = sg.Qall; p.qrow_bytes = qrow; p.n_total = N;
+        p.fin2 = sg.dv0 ? 1 : 0; p.dv0_out = sg.dv0; p.neg0_out = sg.dx0;
+    }
     int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
     if (cap > kMaxGrid) cap = kMaxGrid;
     const int grid = (int)(p.tok_tiles < cap ? p.tok_tiles : cap);

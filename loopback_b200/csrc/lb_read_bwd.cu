@@ -36,6 +36,7 @@ struct BwdSmemTail {
     int abort_flag;
     float xch[2][kBwdMaxNcw];                   // partial g.v of the token's warps, double buffered by source
     float fin[kBwdMaxNcw];                      // per token: coefficient of the key-scale term of the finalised source
+    float fin0[kBwdMaxNcw];                     // ... and of update 0, which the step-1 backward finishes as well
     uint64_t full[kBwdMaxStages];
     uint64_t empty[kBwdMaxStages];
     uint64_t sfull[2];
@@ -46,9 +47,9 @@ struct BwdSmemTail {
 __host__ __device__ inline int bwd_npad(int n) { return (n + 3) & ~3; }
 __host__ __device__ inline size_t bwd_table_floats(int n, int bt) { return (size_t)bwd_npad(n) * bt; }
 
-size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec) {
-    size_t stage = (size_t)fr * ncw * kChunkBytes;
-    size_t tables = (2 * kBwdTables + 1) * bwd_table_floats(n, ncw / wpt) * sizeof(float);
+size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec, int earlier_steps, int qrow_bytes) {
+    size_t stage = (size_t)fr * ncw * kChunkBytes + (size_t)qrow_bytes;
+    size_t tables = ((2 * kBwdTables + 1) * bwd_table_floats(n, ncw / wpt) + 8 * bwd_table_floats(earlier_steps, ncw / wpt)) * sizeof(float);
     size_t slots = (size_t)fr * vec * sizeof(float) * ncw * 32;
     size_t qrow = (size_t)fr * wpt * 32 * vec * sizeof(float);       // the query, padded to whole chunks
     return 1024 + stages * stage + ((tables + 15) & ~size_t(15)) + slots + qrow + sizeof(BwdSmemTail) + 64;
@@ -56,9 +57,13 @@ size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec)
 
 // SOLO: one warp owns a token's whole row (WPT == 1): no exchange between warps, no named barriers, a one-source-deep
 // pipeline; g stays packed in registers (unpacked where it is used) to leave room for 4 fragments per lane.
-// STEP: the backward of a whole step (lb_step_bwd): always finalising, the newest update's gradient leaves as the
-// gradients of the block output and input instead of being stored.
-template <typename T, int FR, int NCW, bool SOLO, bool STEP>
+// MODE 0: the plain backward of a read (lb_read_bwd, lb_read_bwd_final, lb_combine_bwd).
+// MODE 1 (STEP): the backward of a whole step (lb_step_bwd): always finalising, the newest update's gradient leaves as
+//   the gradients of the block output and input instead of being stored.
+// MODE 2 (DEFER): lb_step_bwd_deferred. No gradient stack is read or written: phase 2 forms the finished gradient of the
+//   newest update from the upstream-gradient rows g and the per-source scalars that the backward steps before this one
+//   left behind (this step leaves its own), and hands it out as in MODE 1.
+template <typename T, int FR, int NCW, bool SOLO, int MODE>
 __global__ void __launch_bounds__((NCW + 1 + kBwdScalarWarps) * 32, 1)
 read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
                 const __grid_constant__ CUtensorMap tmDV, const __grid_constant__ CUtensorMap tmH0, ReadBwdParams p) {
@@ -69,22 +74,29 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     constexpr int BW = kChunkBytes / S::kBytes;
     constexpr uint32_t kStageBytes = FR * NCW * kChunkBytes;
     constexpr int kConsumerThreads = NCW * 32;
+    constexpr bool STEP = MODE >= 1, DEFER = MODE == 2;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NS = p.stages, n = p.n, WPT = SOLO ? 1 : p.wpt, BT = NCW / WPT;
     const uint32_t tfl4 = (uint32_t)bwd_table_floats(n, BT) * 4u;      // bytes of one table
+    const int J = DEFER ? p.n_total - n : 0;                           // backward steps that ran before this one
+    const uint32_t ftl4 = (uint32_t)bwd_table_floats(J, BT) * 4u;      // bytes of one table of their scalars
 
     // shared-window addresses of the regions of the dynamic shared memory
     extern __shared__ uint8_t smem_raw[];
     const uint32_t stages_a = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t tables_a = stages_a + (uint32_t)NS * kStageBytes;
+    // a stage: one tile; in the deferred form a g tile travels with the query row of its step right behind it
+    const uint32_t pitch = DEFER ? kStageBytes + (uint32_t)p.qrow_bytes : kStageBytes;
+    const uint32_t tables_a = stages_a + (uint32_t)NS * pitch;
     const uint32_t gdkq_a = tables_a + 2u * kBwdTables * tfl4;
-    const uint32_t slots_a = (gdkq_a + tfl4 + 15u) & ~15u;
+    const uint32_t ft_a = gdkq_a + tfl4;                               // DEFER: 2 buffers x 4 tables (w, kq; w, kq of update 0)
+    const uint32_t slots_a = (ft_a + (DEFER ? 8u * ftl4 : 0u) + 15u) & ~15u;
     const uint32_t qsm_a = slots_a + (uint32_t)(FR * V4 * kConsumerThreads) * 16u;
     const uint32_t tail_a = (qsm_a + (uint32_t)(FR * WPT * 32 * V4) * 16u + 15u) & ~15u;
     const uint32_t c0_a = tail_a + offsetof(BwdSmemTail, c0), lc_a = tail_a + offsetof(BwdSmemTail, lc);
     const uint32_t mass_a = tail_a + offsetof(BwdSmemTail, mass), abort_a = tail_a + offsetof(BwdSmemTail, abort_flag);
     const uint32_t xch_a = tail_a + offsetof(BwdSmemTail, xch), fin_a = tail_a + offsetof(BwdSmemTail, fin);
+    const uint32_t fin0_a = tail_a + offsetof(BwdSmemTail, fin0);
     const uint32_t full_a = tail_a + offsetof(BwdSmemTail, full), empty_a = tail_a + offsetof(BwdSmemTail, empty);
     const uint32_t sfull_a = tail_a + offsetof(BwdSmemTail, sfull), sempty_a = tail_a + offsetof(BwdSmemTail, sempty);
 
@@ -118,7 +130,9 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     const long long n_tiles = p.tok_tiles;
     // the old h0 gradient comes as one more tile (one-warp-per-token shapes; the others leave h0's gradient to a kernel of its own)
     const bool dh0_rmw = STEP && SOLO && p.dh0 != nullptr && p.dh0_accum != 0;
-    const int items_per_tile = 1 + n + (p.accum ? n : 0) + (dh0_rmw ? 1 : 0);
+    const bool fin2 = DEFER && p.fin2 != 0;       // also finish update 0 (the step-1 backward)
+    const int items_per_tile = DEFER ? 1 + (dh0_rmw ? 1 : 0) + n + J + (fin2 ? 1 + J : 0)
+                                     : 1 + n + (p.accum ? n : 0) + (dh0_rmw ? 1 : 0);
     // stage layout: token-major [t][chunk][512 B] when one 4-D TMA box fills a stage, chunk-major [chunk][t][512 B]
     // when the row is fetched chunk by chunk
     const int tstride = p.rank4 ? p.chunks : 1, cstride = p.rank4 ? 1 : BT;
@@ -153,10 +167,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             const uint32_t tb = tables_a + buf * kBwdTables * tfl4 + t4;
             const uint32_t gk = gdkq_a + t4;
             // ---- g tile -> registers (as fp32 pairs)
-            float2 g2[SOLO ? 1 : FR][P];
-            uint4 gpk[SOLO ? FR : 1];
+            // (the one-warp-per-token shapes keep g packed and unpack it where it is used, to leave room for 4 fragments
+            // per lane; unpacked it costs the 4-fragment shape 200 bytes of spills)
+            constexpr bool PACKG = SOLO;
+            float2 g2[PACKG ? 1 : FR][P];
+            uint4 gpk[PACKG ? FR : 1];
             auto load_g = [&](int k, float2 (&gf)[P]) {          // g fragment k as fp32 pairs
-                if constexpr (SOLO) S::unpack2(gpk[k], gf);
+                if constexpr (PACKG) S::unpack2(gpk[k], gf);
                 else {
 #pragma unroll
                     for (int e = 0; e < P; ++e) gf[e] = g2[k][e];
@@ -164,15 +181,25 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             };
             {
                 if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+                const uint32_t sb = stages_a + (uint32_t)st * pitch;
 #pragma unroll
                 for (int k = 0; k < FR; ++k) {
                     const uint4 u = valid[k] ? lds_v4(sb + foff[k]) : zero4;
-                    if constexpr (SOLO) gpk[k] = u; else S::unpack2(u, g2[k]);
+                    if constexpr (PACKG) gpk[k] = u; else S::unpack2(u, g2[k]);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_a + 8u * st);
                 if (++st == NS) { st = 0; ph ^= 1u; }
+            }
+            if constexpr (DEFER) {
+                // the upstream gradient is kept for the backward steps that follow (autograd frees its own copy)
+                T *grow = reinterpret_cast<T *>(p.Gst) + ((long long)(n - 1) * p.n_tok + tok) * (long long)p.d + chunk0 * BW + lane * VEC;
+#pragma unroll
+                for (int k = 0; k < FR; ++k) {
+                    uint4 u;
+                    if constexpr (PACKG) u = gpk[k]; else u = S::pack2v(g2[k]);
+                    if (alive && tok_in && (chunk0 + k) * BW + lane * VEC < p.d) st_global_v4(grow + k * BW, u);
+                }
             }
             if (STEP && SOLO && p.dh0 != nullptr) {
                 // the read closed an iteration (base = h + beta (h0 - h)): h0's share of g, round(beta g), leaves at
@@ -181,7 +208,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 uint32_t sb0 = 0;
                 if (dh0_rmw) {
                     if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                    sb0 = stages_a + (uint32_t)st * kStageBytes;
+                    sb0 = stages_a + (uint32_t)st * pitch;
                 }
                 const float2 b2 = make_float2(p.beta, p.beta);
 #pragma unroll
@@ -223,7 +250,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 float dnew = 0.f;
                 if (i < n) {
                     if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                    const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+                    const uint32_t sb = stages_a + (uint32_t)st * pitch;
 #pragma unroll
                     for (int k = 0; k < FR; ++k) raw[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
                     __syncwarp();
@@ -305,6 +332,15 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     sts_f32(gk + i4, dz * ri * inv);
                     const float drtot = lds_f32(tb + 5u * tfl4 + i4) + dz * lds_f32(tb + 4u * tfl4 + i4);
                     if (p.finalize && i == n - 1) sts_f32(fin_a + t4, drtot * (-(ri * ri * ri)) / (float)p.d);
+                    if constexpr (DEFER) {
+                        if (fin2 && i == 0) sts_f32(fin0_a + t4, drtot * (-(ri * ri * ri)) / (float)p.d);
+                        if (alive && tok_in && i < n - 1) {
+                            // what the later finishing of update i needs of this step: its coefficient of g and of q
+                            const long long e = ((long long)(n - 1) * p.n_total + i) * p.n_tok + tok;
+                            p.Wt[e] = lds_f32(tb + 3u * tfl4 + i4);
+                            p.KQt[e] = dz * ri * inv;
+                        }
+                    }
                     if (alive && tok_in) {
                         p.dR[(long long)i * p.n_tok + tok] = drtot;
                         if (p.tc_prev == nullptr) p.dcbar[tok * n + i] = -gd;
@@ -326,7 +362,95 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     q2[k][2 * e4 + 1] = make_float2(q4.z, q4.w);
                 }
             }
-            if constexpr (STEP) {
+            if constexpr (DEFER) {
+                // The finished gradient of an update, formed in one go:
+                //   dV = sum over the steps s' that read it (this one, then the J that ran their backward before it) of
+                //        w_{s'} g_{s'} + kq_{s'} q_{s'},   plus its key-scale term,
+                // accumulated in fp32 and rounded once. g_{s'} comes from the g stack through the ring, the two scalars
+                // from the tables the scalar warps prepared, the query row from global memory (one tile ahead).
+                const uint32_t ftb = ft_a + buf * 4u * ftl4 + t4;
+                auto finish = [&](auto main_tag, int src, uint32_t ftab, const uint4 (&vfr)[FR], float kf) {
+                    constexpr bool MAIN = decltype(main_tag)::value;
+                    const uint32_t s4 = (uint32_t)src * BT4;
+                    const float w_own = lds_f32(tb + 3u * tfl4 + s4), kq_own = lds_f32(gk + s4);
+                    const float2 w2 = make_float2(w_own, w_own), kq2 = make_float2(kq_own, kq_own), kf2 = make_float2(kf, kf);
+                    float2 acc[FR][P];
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) {
+                        float2 gf[P], vf[P];
+                        load_g(k, gf);
+                        S::unpack2(vfr[k], vf);
+#pragma unroll
+                        for (int e = 0; e < P; ++e)
+                            acc[k][e] = __ffma2_rn(kf2, vf[e], __ffma2_rn(w2, gf[e], __fmul2_rn(kq2, q2[k][e])));
+                    }
+                    for (int j = 0; j < J; ++j) {
+                        if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                        const uint32_t sb = stages_a + (uint32_t)st * pitch;
+                        const float fw = lds_f32(ftab + (uint32_t)j * BT4), fkq = lds_f32(ftab + ftl4 + (uint32_t)j * BT4);
+                        const float2 fw2 = make_float2(fw, fw), fkq2 = make_float2(fkq, fkq);
+#pragma unroll
+                        for (int k = 0; k < FR; ++k) {
+                            const int col = (chunk0 + k) * BW + lane * VEC;
+                            const bool in_row = valid[k] && col < p.d;
+                            float2 gf[P];
+                            S::unpack2(valid[k] ? lds_v4(sb + foff[k]) : zero4, gf);
+#pragma unroll
+                            for (int e4 = 0; e4 < V4; ++e4) {
+                                const float4 q4 = in_row ? lds_f4(sb + kStageBytes + 4u * (uint32_t)col + 16u * e4)
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+                                acc[k][2 * e4] = __ffma2_rn(fkq2, make_float2(q4.x, q4.y), acc[k][2 * e4]);
+                                acc[k][2 * e4 + 1] = __ffma2_rn(fkq2, make_float2(q4.z, q4.w), acc[k][2 * e4 + 1]);
+                            }
+#pragma unroll
+                            for (int e = 0; e < P; ++e) acc[k][e] = __ffma2_rn(fw2, gf[e], acc[k][e]);
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                        if (++st == NS) { st = 0; ph ^= 1u; }
+                    }
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) {
+                        const uint4 res = S::pack2v(acc[k]);
+                        const int col = (chunk0 + k) * BW + lane * VEC;
+                        const bool live = alive && tok_in && col < p.d;
+                        const long long off = tok * (long long)p.d + col;
+                        if constexpr (MAIN) {
+                            if (live) st_global_v4(reinterpret_cast<T *>(p.neg_out) + off, S::negate(res));
+                            float2 gf[P];
+                            load_g(k, gf);
+                            if (p.blend) {
+                                const float2 b2 = make_float2(p.beta, p.beta);
+                                float2 bg[P];
+#pragma unroll
+                                for (int e = 0; e < P; ++e) bg[e] = __fmul2_rn(b2, gf[e]);
+                                S::unpack2(S::pack2v(bg), bg);                  // rounded to the storage type
+#pragma unroll
+                                for (int e = 0; e < P; ++e) gf[e] = __fadd2_rn(gf[e], make_float2(-bg[e].x, -bg[e].y));
+                            }
+                            if (live) st_global_v4(reinterpret_cast<T *>(p.dh_out) + off, S::accum(res, gf));
+                        } else {
+                            if (live) {
+                                st_global_v4(reinterpret_cast<T *>(p.dv0_out) + off, res);
+                                st_global_v4(reinterpret_cast<T *>(p.neg0_out) + off, S::negate(res));
+                            }
+                        }
+                    }
+                };
+                finish(std::true_type{}, n - 1, ftb, SOLO ? v1 : v2, lds_f32(fin_a + t4));
+                if (fin2) {
+                    // update 0 has no step of its own: its fragments come back through the ring, then the same rows of g again
+                    if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
+                    const uint32_t sb = stages_a + (uint32_t)st * pitch;
+                    uint4 v0f[FR];
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) v0f[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                    if (++st == NS) { st = 0; ph ^= 1u; }
+                    finish(std::false_type{}, 0, ftb + 2u * ftl4, v0f, lds_f32(fin0_a + t4));
+                }
+            } else if constexpr (STEP) {
                 T *dvrow = reinterpret_cast<T *>(p.dV) + tok * (long long)p.d + chunk0 * BW + lane * VEC;
                 const long long src_stride = p.n_tok * (long long)p.d;
                 // One source of phase 2. FINAL (compile time) is the newest source of a finalising read, peeled out of the
@@ -339,7 +463,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     uint4 prev[FR];
                     if (p.accum) {
                         if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                        const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+                        const uint32_t sb = stages_a + (uint32_t)st * pitch;
 #pragma unroll
                         for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
                         __syncwarp();
@@ -408,7 +532,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     uint4 prev[FR];
                     if (p.accum) {
                         if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
-                        const uint32_t sb = stages_a + (uint32_t)st * kStageBytes;
+                        const uint32_t sb = stages_a + (uint32_t)st * pitch;
 #pragma unroll
                         for (int k = 0; k < FR; ++k) prev[k] = valid[k] ? lds_v4(sb + foff[k]) : zero4;
                         __syncwarp();
@@ -470,11 +594,17 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
         if (lane == 0) {
             tma_prefetch_desc(&tmV);
             tma_prefetch_desc(&tmG);
-            if (p.accum) tma_prefetch_desc(&tmDV);
+            if (p.accum || DEFER) tma_prefetch_desc(&tmDV);
             if (dh0_rmw) tma_prefetch_desc(&tmH0);
             const int v0 = dh0_rmw ? 2 : 1;                      // first V item; item 1 is the h0-gradient tile if any
             // the order in which phase 2 wants the old gradients: a finalising read takes the newest source first
-            auto dv_source = [&](int j) { return STEP && SOLO ? (j == 0 ? n - 1 : j - 1) : j; };
+            // which slice of the second stack an item past the sources asks for. Plain / step: the old gradient of source
+            // j, a one-warp-per-token step taking the newest first. Deferred: the g row of the j-th earlier backward step
+            // (slice n + j), and after update 0's fragments (item J) the same rows once more.
+            auto dv_source = [&](int j) {
+                if (DEFER) return n + (j > J ? j - J - 1 : j);
+                return MODE == 1 && SOLO ? (j == 0 ? n - 1 : j - 1) : j;
+            };
             int st = 0; uint32_t ph = 0;
             int issued = 0;
             bool ok = true;
@@ -486,12 +616,18 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                         ok = false;
                         break;
                     }
-                    const uint32_t sb = stages_a + (uint32_t)st * kStageBytes, fb = full_a + 8u * st;
-                    mbar_arrive_expect_tx(fb, (uint32_t)(nch * BT * kChunkBytes));
+                    const uint32_t sb = stages_a + (uint32_t)st * pitch, fb = full_a + 8u * st;
+                    // deferred form: which earlier backward step a g item belongs to (-1: not a g item)
+                    int gj = -1;
+                    if (DEFER && item >= v0 + n && item != v0 + n + J) gj = item - v0 - n - (item > v0 + n + J ? J + 1 : 0);
+                    mbar_arrive_expect_tx(fb, (uint32_t)(nch * BT * kChunkBytes) + (gj >= 0 ? (uint32_t)p.qrow_bytes : 0u));
+                    if (gj >= 0)        // the query of step n + gj (row n - 1 + gj) rides behind the tile
+                        bulk_load(sb + kStageBytes, p.Qall + (long long)(n - 1 + gj) * p.d, (uint32_t)p.qrow_bytes, fb);
                     if (p.rank4) {
                         if (item == 0) tma_load_3d(sb, &tmG, fb, 0, 0, tok0);
                         else if (item < v0) tma_load_3d(sb, &tmH0, fb, 0, 0, tok0);
                         else if (item < v0 + n) tma_load_4d(sb, &tmV, fb, 0, 0, tok0, item - v0);
+                        else if (DEFER && item == v0 + n + J) tma_load_4d(sb, &tmV, fb, 0, 0, tok0, 0);
                         else tma_load_4d(sb, &tmDV, fb, 0, 0, tok0, dv_source(item - v0 - n));
                     } else {
                         for (int c = 0; c < nch; ++c) {
@@ -499,6 +635,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                             if (item == 0) tma_load_2d(dst, &tmG, fb, c * BW, tok0);
                             else if (item < v0) tma_load_2d(dst, &tmH0, fb, c * BW, tok0);
                             else if (item < v0 + n) tma_load_3d(dst, &tmV, fb, c * BW, tok0, item - v0);
+                            else if (DEFER && item == v0 + n + J) tma_load_3d(dst, &tmV, fb, c * BW, tok0, 0);
                             else tma_load_3d(dst, &tmDV, fb, c * BW, tok0, dv_source(item - v0 - n));
                         }
                     }
@@ -551,19 +688,37 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                 sts_f32(o + 4u * tfl4, (lg - lci) / r);
                 sts_f32(o + 5u * tfl4, drp);
             }
+            if constexpr (DEFER) {
+                // the scalars the earlier backward steps left for the update(s) this step finishes: lanes over tokens
+                const uint32_t ft = ft_a + buf * 4u * ftl4;
+                for (int idx = sw * 32 + lane; idx < BT * J; idx += kBwdScalarWarps * 32) {
+                    const int j = idx / BT, t = idx - j * BT;
+                    long long tok = tile * BT + t;
+                    if (tok >= p.n_tok) tok = p.n_tok - 1;
+                    const long long e = ((long long)(n + j) * p.n_total + (n - 1)) * p.n_tok + tok;
+                    sts_f32(ft + 4u * (uint32_t)idx, __ldg(p.Wt + e));
+                    sts_f32(ft + ftl4 + 4u * (uint32_t)idx, __ldg(p.KQt + e));
+                    if (fin2) {
+                        const long long e0 = (long long)(n + j) * p.n_total * p.n_tok + tok;
+                        sts_f32(ft + 2u * ftl4 + 4u * (uint32_t)idx, __ldg(p.Wt + e0));
+                        sts_f32(ft + 3u * ftl4 + 4u * (uint32_t)idx, __ldg(p.KQt + e0));
+                    }
+                }
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(sfull_a + 8u * buf);
         }
     }
 }
 
-template <typename T, int FR, int NCW, bool SOLO, bool STEP>
+template <typename T, int FR, int NCW, bool SOLO, int MODE>
 static cudaError_t launch_bwd(const CUtensorMap &tmV, const CUtensorMap &tmG, const CUtensorMap &tmDV,
                               const CUtensorMap &tmH0, const ReadBwdParams &p, int grid, cudaStream_t stream) {
-    size_t smem = read_bwd_smem_bytes(FR, NCW, p.wpt, p.stages, p.n, Store<T>::kVec);
-    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR, NCW, SOLO, STEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    size_t smem = read_bwd_smem_bytes(FR, NCW, p.wpt, p.stages, p.n, Store<T>::kVec, MODE == 2 ? p.n_total - p.n : 0,
+                                      MODE == 2 ? p.qrow_bytes : 0);
+    cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR, NCW, SOLO, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    read_bwd_kernel<T, FR, NCW, SOLO, STEP><<<grid, (NCW + 1 + kBwdScalarWarps) * 32, smem, stream>>>(tmV, tmG, tmDV, tmH0, p);
+    read_bwd_kernel<T, FR, NCW, SOLO, MODE><<<grid, (NCW + 1 + kBwdScalarWarps) * 32, smem, stream>>>(tmV, tmG, tmDV, tmH0, p);
     return cudaGetLastError();
 }
 
@@ -574,8 +729,9 @@ cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, 
     // one warp per token (SOLO): 8 x {1,2,3,4}
 #define LB_BWD_CASE(TT, F, W, SOLO_) \
     if (fr == F && ncw == W && (p.wpt == 1) == SOLO_)                                                             \
-        return p.dh_out ? launch_bwd<TT, F, W, SOLO_, true>(tmV, tmG, tmDV, tmH0, p, grid, stream)                  \
-                        : launch_bwd<TT, F, W, SOLO_, false>(tmV, tmG, tmDV, tmH0, p, grid, stream);
+        return p.Gst    ? launch_bwd<TT, F, W, SOLO_, 2>(tmV, tmG, tmDV, tmH0, p, grid, stream)                     \
+             : p.dh_out ? launch_bwd<TT, F, W, SOLO_, 1>(tmV, tmG, tmDV, tmH0, p, grid, stream)                     \
+                        : launch_bwd<TT, F, W, SOLO_, 0>(tmV, tmG, tmDV, tmH0, p, grid, stream);
 #define LB_BWD_ALL(TT)                                                                                         \
     LB_BWD_CASE(TT, 1, 16, false) LB_BWD_CASE(TT, 2, 16, false) LB_BWD_CASE(TT, 1, 12, false)                   \
     LB_BWD_CASE(TT, 2, 12, false) LB_BWD_CASE(TT, 1, 8, false) LB_BWD_CASE(TT, 2, 8, false)                     \

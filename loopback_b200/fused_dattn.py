@@ -304,7 +304,8 @@ class DattnStack:
     are when the stack is built, i.e. for one forward pass."""
     __slots__ = ("V", "R", "dV", "dR", "n_steps", "n_tok", "d", "eps", "Q", "QT", "DOTS", "r_done", "_scratch",
                  "fuse_final", "_scale_done", "_neg", "_last_write", "_dq", "_dh0", "_first_step", "_first_blend",
-                 "d_done", "defer_writes", "_pending", "_small")
+                 "d_done", "defer_writes", "_pending", "_small", "deferred_grads", "_da", "_G", "_Wt", "_KQt", "_dv0",
+                 "_n_step_nodes")
 
     def __init__(self, n_steps: int, shape, dtype, device, query=None, eps: float = 1e-6):
         b, t, d = shape
@@ -344,6 +345,14 @@ class DattnStack:
         self._last_write = None
         self._dq = self._dh0 = None
         self._first_step = self._first_blend = None
+        # Deferred gradient accumulation (lb_step_bwd_deferred): when every step of the pass is a FusedStepStk node and
+        # the backward starts at the last step, no gradient stack dV is kept at all; each step's backward stores its
+        # upstream gradient (_G, a stack like V) and two scalars per older source (_Wt, _KQt) and forms the finished
+        # gradient of its own update from what the later steps left. Decided by the pass's first backward (_da).
+        self.deferred_grads = True
+        self._da = None
+        self._G = self._Wt = self._KQt = self._dv0 = None
+        self._n_step_nodes = 0
         if query is not None:
             self.Q = query.detach().float().contiguous()
             self.DOTS = torch.empty((max(1, self.Q.shape[0]), self.n_steps, b * t), dtype=torch.float32, device=device)
@@ -427,7 +436,10 @@ class _WriteDelta(torch.autograd.Function):
         neg = stack._neg[s] if stack is not None else None
         if neg is not None:
             stack._neg[s] = None
-            if stack.dV is not None and g.data_ptr() == stack.dV[s].data_ptr() and g.shape == neg.shape:
+            done = stack._dv0 if stack._da else (stack.dV[s] if stack.dV is not None else None)
+            if stack._da:
+                stack._dv0 = None
+            if done is not None and g.data_ptr() == done.data_ptr() and g.shape == neg.shape:
                 return None, None, g, neg            # the final read of update s already wrote -dV[s]
         gc = g.contiguous()
         dx = torch.empty_like(gc)
@@ -453,7 +465,7 @@ class _RstdStk(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gr: torch.Tensor):
         stack, s, x = ctx.stack, ctx.s, ctx.x
-        if stack.dV is None:
+        if stack.dV is None and not stack._da:
             raise RuntimeError("delta_attnres stacked read: the scale's backward ran before any read's backward")
         grc = gr.contiguous().float()
         if stack._scale_done[s]:
@@ -465,11 +477,14 @@ class _RstdStk(torch.autograd.Function):
                 stack._neg[s] = None                 # the negated copy no longer matches
         if grc is not None:
             xc = x.detach().contiguous()
-            dv_s = stack.dV[s]
+            dv_s = stack._dv0 if stack._da else stack.dV[s]
             with torch.cuda.device(xc.device):
                 check(_lib.lib().lb_rstd_bwd_acc(ptr(xc), ptr(stack.R[s]), ptr(grc), ptr(dv_s), stack.n_tok, stack.d,
                                                  dtype_code(xc.dtype), stream_ptr()), "stacked rstd backward")
-        out = _alias(stack.dV, s)
+        if stack._da:                     # no gradient stack: update 0's gradient was handed over by the step-1 backward
+            out = stack._dv0
+        else:
+            out = _alias(stack.dV, s)
         ctx.stack = ctx.x = None          # release the stack from this node
         return None, None, out, None
 
@@ -658,6 +673,7 @@ class FusedStepStk(torch.autograd.Function):
                                             stack.n_steps, n, dtype_code(stack.V.dtype), stream_ptr()), "combine forward")
         if save:
             ctx.save_for_backward(qc, tcp, c0c, lg, lse, lse0)
+            stack._n_step_nodes += 1
             if stack._first_step is None:
                 stack._first_step = int(step)
             if h0 is not None and ctx.needs_input_grad[5] and stack._first_blend is None:
@@ -674,7 +690,10 @@ class FusedStepStk(torch.autograd.Function):
         qc, tcp, c0c, lg, lse, lse0 = ctx.saved_tensors
         stack, step, n = ctx.stack, ctx.step, ctx.n
         d, n_tok, dev = stack.d, stack.n_tok, stack.V.device
-        accum = stack.grads()
+        N = stack.n_steps
+        if stack._da is None:                 # the pass's first backward decides how the updates' gradients are formed
+            stack._da = bool(stack.deferred_grads and step == N - 1 and stack.dV is None and stack.dR is None
+                             and stack._n_step_nodes == N - 1 and stack.Q is not None and stack.Q.shape[0] == N - 1)
         g = g.contiguous()
         gt_c = None if gt is None else gt.reshape(n_tok, n).float().contiguous()
         if stack._dq is None:
@@ -688,15 +707,39 @@ class FusedStepStk(torch.autograd.Function):
         dh = torch.empty(ctx.shape, device=dev, dtype=stack.V.dtype)
         dx = torch.empty(ctx.shape, device=dev, dtype=stack.V.dtype)
         dtc = torch.empty((n_tok, n - 1), device=dev, dtype=torch.float32)
-        # V, the older updates' gradients (read + written), g and the newest update's gradient in, dh and dx out, the
-        # loop input's gradient read + written at an iteration's end
-        units = n + ((2 * (n - 1) + 1) if accum else (n - 1)) + 1 + 2 + ((2 if dh0_accum else 1) if dh0 is not None else 0)
-        with torch.cuda.device(dev), _timed("read_bwd", n, units):
-            check(_lib.lib().lb_step_bwd(ptr(stack.V), ptr(stack.R), ptr(stack.dV), ptr(stack.dR), ptr(qc), ptr(g),
-                                         ptr(gt_c), ptr(tcp), ctx.lam, ptr(c0c), ptr(lg), ptr(lse), ptr(lse0), ptr(dtc),
-                                         ptr(stack._dq[step - 1]), ptr(stack.scratch()), ptr(dh), ptr(dx), ptr(dh0),
-                                         int(dh0_accum), int(ctx.blend), ctx.beta, n_tok, d, stack.n_steps, n,
-                                         int(bool(accum)), dtype_code(stack.V.dtype), stream_ptr()), "step backward")
+        dh0_units = (2 if dh0_accum else 1) if dh0 is not None else 0
+        if stack._da:
+            first = stack.dR is None
+            if first:
+                stack.dR = torch.empty_like(stack.R)
+                stack._G = torch.empty_like(stack.V)
+                stack._Wt = torch.empty((N, N, n_tok), device=dev, dtype=torch.float32)
+                stack._KQt = torch.empty((N, N, n_tok), device=dev, dtype=torch.float32)
+            dv0 = dx0 = None
+            if step == 1:                     # update 0 has no step of its own: this backward finishes it too
+                dv0 = torch.empty(ctx.shape, device=dev, dtype=stack.V.dtype)
+                dx0 = torch.empty(ctx.shape, device=dev, dtype=stack.V.dtype)
+                stack._dv0, stack._neg[0], stack._scale_done[0] = dv0, dx0, True
+            # g in and kept, V, the g rows of the later steps, dh and dx out (update 0: its row, those g rows again, 2 out)
+            units = 1 + 1 + n + (N - n) + 2 + dh0_units + ((1 + (N - n) + 2) if step == 1 else 0)
+            with _on(dev), _timed("read_bwd", n, units):
+                check(_lib.lib().lb_step_bwd_deferred(
+                    ptr(stack.V), ptr(stack.R), ptr(stack._G), ptr(stack.dR), ptr(stack._Wt), ptr(stack._KQt), ptr(stack.Q),
+                    ptr(g), ptr(gt_c), ptr(tcp), ctx.lam, ptr(c0c), ptr(lg), ptr(lse), ptr(lse0), ptr(dtc),
+                    ptr(stack._dq[step - 1]), ptr(stack.scratch()), ptr(dh), ptr(dx), ptr(dh0), int(dh0_accum),
+                    int(ctx.blend), ctx.beta, ptr(dv0), ptr(dx0), n_tok, d, N, n, int(first), dtype_code(stack.V.dtype),
+                    stream_ptr()), "step backward (deferred)")
+        else:
+            accum = stack.grads()
+            # V, the older updates' gradients (read + written), g and the newest update's gradient in, dh and dx out, the
+            # loop input's gradient read + written at an iteration's end
+            units = n + ((2 * (n - 1) + 1) if accum else (n - 1)) + 1 + 2 + dh0_units
+            with _on(dev), _timed("read_bwd", n, units):
+                check(_lib.lib().lb_step_bwd(ptr(stack.V), ptr(stack.R), ptr(stack.dV), ptr(stack.dR), ptr(qc), ptr(g),
+                                             ptr(gt_c), ptr(tcp), ctx.lam, ptr(c0c), ptr(lg), ptr(lse), ptr(lse0), ptr(dtc),
+                                             ptr(stack._dq[step - 1]), ptr(stack.scratch()), ptr(dh), ptr(dx), ptr(dh0),
+                                             int(dh0_accum), int(ctx.blend), ctx.beta, n_tok, d, N, n,
+                                             int(bool(accum)), dtype_code(stack.V.dtype), stream_ptr()), "step backward")
         dquery = dh0_out = None
         if step == stack._first_step:             # the earliest step runs last: the pass's query gradient is complete
             dquery, stack._dq = stack._dq.to(ctx.q_dtype), None

@@ -491,9 +491,10 @@ def reference_combine(cell, FD, proposal, h0, deltas, coeffs, prior_coeffs, loop
 
 
 # how the chain calls the read: the cell's fast path (prologue inside the kernels, one autograd node per step:
-# FusedStepStk), the same without the step node (FusedCombineStk), the cell with its prologue in torch
+# FusedStepStk, no gradient stack: lb_step_bwd_deferred), the same with the gradient stack accumulated in place
+# (lb_step_bwd), the same without the step node (FusedCombineStk), the cell with its prologue in torch
 # (FusedDattnReadStk, the entry point the reference trainer calls), the reference's own combine restated above
-COMBINE_PATHS = ["fused", "fused_combine", "dropin", "reference_combine"]
+COMBINE_PATHS = ["fused", "fused_rmw", "fused_combine", "dropin", "reference_combine"]
 
 
 def chain_gpu(FD, h0, D, Q, Gu, K, R, beta, eps, scores, with_grad, list_layout=False, path="fused", use_keys=True):
@@ -502,8 +503,9 @@ def chain_gpu(FD, h0, D, Q, Gu, K, R, beta, eps, scores, with_grad, list_layout=
     N = K * R
     b, t, d = h0.shape
     cell = LoopDeltaAttnRes(d, R, K, beta=beta, eps=eps).cuda()
-    cell.fuse_prologue = path in ("fused", "fused_combine")
-    cell.fuse_step = path == "fused"
+    cell.fuse_prologue = path in ("fused", "fused_rmw", "fused_combine")
+    cell.fuse_step = path in ("fused", "fused_rmw")
+    cell.deferred_grads = path == "fused"
     with torch.no_grad():
         if N > 1:
             cell.query.copy_(Q[:N - 1].cuda())
@@ -603,8 +605,8 @@ def test_bf16_chain_teacher_forced(FD, L, d, K, R, n_tok, write_kernel, combine)
     L.set_option("write_tt", write_kernel)
     h0, D, Q, Gu = cases.chain_inputs(1, n_tok, d, K, R, seed=d + K, dtype=torch.bfloat16, sigma_d=0.3)
     cell = LoopDeltaAttnRes(d, R, K, beta=0.75, eps=1e-6).cuda()
-    cell.fuse_prologue = combine in ("fused", "fused_combine")
-    cell.fuse_step = combine == "fused"
+    cell.fuse_prologue = combine in ("fused", "fused_rmw", "fused_combine")
+    cell.fuse_step = combine in ("fused", "fused_rmw")
     with torch.no_grad():
         cell.query.copy_(Q[:N - 1].cuda())
     stack = cell.new_stack((1, n_tok, d), torch.bfloat16, "cuda", scores=True)
