@@ -549,9 +549,17 @@ def main():
                     "traffic_source": "ncu dram bytes of an 8192-token capture of the same kernel and row size "
                                       "(profiles/step_bwd_cfg2_8192tok.md, read_fwd_cfg2_8192tok.md, "
                                       "write_mma_cfg2_32768tok.md), scaled by tokens",
-                    "bytes_per_launch_avg": by / cnt, "ms_per_launch_avg": sec * 1e3 / cnt}
+                    "bytes_per_launch_avg": by / cnt, "ms_per_launch_avg": sec * 1e3 / cnt,
+                    "note": "bytes by design of the launches that ran: the deferred step backward reads V (n rows), the "
+                            "g rows of the later steps (N - n) and g, writes g, dh, dx -- N + 3 rows per token and step, "
+                            "where the in-place form moves 3n + 2"}
     pass_units = algorithmic_units(N, w["backward"])
     pass_gbs = pass_units * n_tok * row / (ms_per_step * 1e-3) / 1e9
+    # what this library's launches of one pass move by design (the sum of the launches' own row counts): less than the
+    # formula above where the algorithm needs fewer transfers than the reference's (the deferred backward keeps no
+    # gradient stack: N^2/2 row reads where the in-place accumulation makes N^2 transfers)
+    design_units = sum(u for _, _, u, _, _ in launches) / max(1, args.steps)
+    design_gbs = design_units * n_tok * row / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end: host buffers in, results out, inside the timed region ------------------------------------
     e2e = None
@@ -620,6 +628,10 @@ def main():
                        "pass_algorithmic_units_per_token": pass_units,
                        "pass_algorithmic_gbs": pass_gbs, "pass_frac_of_peak": pass_gbs / peak,
                        "pass_frac_denominator": f"{peak:.1f} GB/s ({peak_kind} copy bandwidth)",
+                       "pass_units_formula": "3N + S + 2(N-1) + S + (2S-N) + (N-1) + N, S = N(N+1)/2 - 1: the transfers of "
+                                             "the reference's algorithm (in-place gradient accumulation)",
+                       "pass_design_units_per_token": design_units, "pass_design_gbs": design_gbs,
+                       "pass_design_frac_of_peak": design_gbs / peak,
                        "harness_adds_ms_per_step": harness_ms, "harness_backward_adds_ms_per_step": harness_bwd_ms,
                        "pass_frac_of_peak_without_harness_adds":
                            pass_units * n_tok * row / ((ms_per_step - harness_total) * 1e-3) / 1e9 / peak,

@@ -199,12 +199,16 @@ int lb_step_bwd(const void *V, const float *R, void *dV, float *dR, const float 
  * (N^2 / 2 row reads, no gradient row written except the outputs). Outputs, blend and dh0 exactly as lb_step_bwd; dR is
  * still accumulated in place (first != 0: written). The step-1 backward (n == 2) also finishes update 0, which has no
  * step of its own: dv0 receives its gradient (key-scale term included), dx0 the negation; NULL otherwise.
- * G [N][n_tok][d] storage dtype; Wt, KQt [N][N][n_tok] fp32; Q [N-1][d] fp32 (every query; this step's is row n - 2).
+ * G [N][n_tok][d] storage dtype; Wt, KQt [N][N][n_tok] fp32; Q [N-1][d] fp32 (every query; this step's is row n - 2);
+ * Qp = the same queries in the order the kernel's lanes read them from shared memory, made once per pass by
+ * lb_permute_queries ([N-1][lb_permuted_query_row_floats(d, dtype)] fp32).
  * Every backward step of a pass must use this form, last step first, for the sums to be complete.
  * More accurate than the in-place accumulation it replaces (autograd's, fused_dattn.py:528-531, rounds after every
  * add); same reference code replaced as lb_step_bwd. */
+size_t lb_permuted_query_row_floats(int d, int dtype);
+int lb_permute_queries(const float *Q, float *Qp, int NQ, int d, int dtype, void *stream);
 int lb_step_bwd_deferred(const void *V, const float *R, void *G, float *dR, float *Wt, float *KQt, const float *Q,
-                         const void *g, const float *gt, const float *tc_prev, float lam, const float *c0, const float *LG,
+                         const float *Qp, const void *g, const float *gt, const float *tc_prev, float lam, const float *c0, const float *LG,
                          const float *LSE, const float *LSE0, float *dtc_prev, float *dq, void *scratch, void *dh, void *dx,
                          void *dh0, int dh0_accum, int blend, float beta, void *dv0, void *dx0, int64_t n_tok, int d, int N,
                          int n, int first, int dtype, void *stream);

@@ -44,7 +44,9 @@ SYMBOLS = {
                             _i, _i, _i, _i, _i, _vp]),
     "lb_step_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                          _f, _i64, _i, _i, _i, _i, _i, _vp]),
-    "lb_step_bwd_deferred": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+    "lb_permuted_query_row_floats": (ctypes.c_size_t, [_i, _i]),
+    "lb_permute_queries": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "lb_step_bwd_deferred": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                   _vp, _vp, _i, _i, _f, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp]),
     "lb_read_bwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
                                  _i, _i, _vp]),

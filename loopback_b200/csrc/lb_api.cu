@@ -525,14 +525,28 @@ int lb_step_bwd(const void *V, const float *R, void *dV, float *dR, const float 
                          N, n, accum, 1, dx, dtype, stream, sg);
 }
 
+size_t lb_permuted_query_row_floats(int d, int dtype) {
+    if (d <= 0 || (dtype != LB_DTYPE_BF16 && dtype != LB_DTYPE_F32)) return 0;
+    return (size_t)chunks_of(d, dtype) * (lb::kChunkBytes / (dtype == LB_DTYPE_BF16 ? 2 : 4));
+}
+
+int lb_permute_queries(const float *Q, float *Qp, int NQ, int d, int dtype, void *stream) {
+    int rc = check_common(0, d, dtype);
+    if (rc) return rc;
+    if (!Q || !Qp || NQ < 0) return fail(LB_ERR_ARG, "lb_permute_queries: NULL pointer or negative size");
+    cudaError_t e = lb::launch_permute_queries(Q, Qp, NQ, d, dtype == LB_DTYPE_BF16 ? 8 : 4,
+                                               (int)lb_permuted_query_row_floats(d, dtype), static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_permute_queries launch");
+}
+
 int lb_step_bwd_deferred(const void *V, const float *R, void *G, float *dR, float *Wt, float *KQt, const float *Q,
-                         const void *g, const float *gt, const float *tc_prev, float lam, const float *c0, const float *LG,
+                         const float *Qp, const void *g, const float *gt, const float *tc_prev, float lam, const float *c0, const float *LG,
                          const float *LSE, const float *LSE0, float *dtc_prev, float *dq, void *scratch, void *dh, void *dx,
                          void *dh0, int dh0_accum, int blend, float beta, void *dv0, void *dx0, int64_t n_tok, int d, int N,
                          int n, int first, int dtype, void *stream) {
     if (n < 2 || !tc_prev) return fail(LB_ERR_ARG, "lb_step_bwd_deferred: needs n >= 2 and the previous read's coefficients");
-    if (!G || !Wt || !KQt || !Q || !dh || !dx) return fail(LB_ERR_ARG, "lb_step_bwd_deferred: NULL pointer");
-    if (!aligned16(G) || !aligned16(Q) || !aligned16(dh) || !aligned16(dx) || (dh0 && !aligned16(dh0)) ||
+    if (!G || !Wt || !KQt || !Q || !Qp || !dh || !dx) return fail(LB_ERR_ARG, "lb_step_bwd_deferred: NULL pointer");
+    if (!aligned16(G) || !aligned16(Q) || !aligned16(Qp) || !aligned16(dh) || !aligned16(dx) || (dh0 && !aligned16(dh0)) ||
         (dv0 && !aligned16(dv0)) || (dx0 && !aligned16(dx0)))
         return fail(LB_ERR_ALIGN, "lb_step_bwd_deferred: G, Q, dh, dx, dh0, dv0 and dx0 must be 16-byte aligned");
     if (((long long)d * 4) % 16) return fail(LB_ERR_ALIGN, "lb_step_bwd_deferred: the query rows must be multiples of 16 bytes");
@@ -542,7 +556,7 @@ int lb_step_bwd_deferred(const void *V, const float *R, void *G, float *dR, floa
     StepGrads sg;
     sg.dh = dh; sg.dh0 = dh0; sg.dh0_accum = dh0 ? dh0_accum : 0; sg.blend = blend ? 1 : 0; sg.beta = beta;
     sg.skip_final_store = 1;
-    sg.deferred = 1; sg.Wt = Wt; sg.KQt = KQt; sg.Qall = Q; sg.dv0 = dv0; sg.dx0 = dx0;
+    sg.deferred = 1; sg.Wt = Wt; sg.KQt = KQt; sg.Qall = Qp; sg.dv0 = dv0; sg.dx0 = dx0;
     return read_bwd_impl(V, R, G, dR, Q + (long long)(n - 2) * d, g, gt, nullptr, tc_prev, lam, c0, LG, LSE, LSE0, dtc_prev, dq,
                          scratch, n_tok, d, N, n, first ? 0 : 1, 1, dx, dtype, stream, sg);
 }
@@ -577,8 +591,13 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     // then tiles of at least 12 KiB, then 2 fragments per warp.
     int ncw = 0, wpt = 0, fr = 0, best_cost = 1 << 30;
     static const int kNcw[3] = {12, 16, 8}, kFrMax[3] = {2, 2, 4};
-    if (nch <= 4 && g_opt.bwd_wpt <= 1 && (g_opt.bwd_warps == 0 || g_opt.bwd_warps == 8)) {
-        ncw = 8; wpt = 1; fr = nch;
+    if (nch <= 4 && g_opt.bwd_wpt <= 1 && (g_opt.bwd_warps == 0 || g_opt.bwd_warps == 8 || g_opt.bwd_warps == 4)) {
+        // 8 consumer warps and one CTA per SM, or ("bwd_warps" = 4) half-size CTAs of 4 consumer warps, two per SM:
+        // two independent pipelines whose phases drift apart
+        // (default: the half-size CTAs for the deferred form's launches that are mostly phase 1, n >= 2N/3: +8 % there,
+        // -3 % where phase 2 dominates)
+        const bool half = g_opt.bwd_warps == 4 || (g_opt.bwd_warps == 0 && sg.deferred && 3 * n >= 2 * N);
+        ncw = half ? 4 : 8; wpt = 1; fr = nch;
     } else {
         for (int a = 0; a < 3; ++a) {
             if (g_opt.bwd_warps && g_opt.bwd_warps != kNcw[a]) continue;
@@ -598,9 +617,10 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     const int vec = dtype == LB_DTYPE_BF16 ? 8 : 4;
     int stages = g_opt.bwd_stages > 0 ? g_opt.bwd_stages : 8;
     if (stages > 12) stages = 12;
-    const int earlier = sg.deferred ? N - n : 0, qrow = sg.deferred ? d * 4 : 0;
-    while (stages > 2 && lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec, earlier, qrow) > kMaxSmem) --stages;
-    if (lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec, earlier, qrow) > kMaxSmem)
+    const int earlier = sg.deferred ? N - n : 0, qrow = sg.deferred ? (int)lb_permuted_query_row_floats(d, dtype) * 4 : 0;
+    const size_t smem_cap = ncw == 4 ? (kMaxSmem - 2048) / 2 : kMaxSmem;      // two half-size CTAs share an SM
+    while (stages > 2 && lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec, earlier, qrow) > smem_cap) --stages;
+    if (lb::read_bwd_smem_bytes(fr, ncw, wpt, stages, n, vec, earlier, qrow) > smem_cap)
         return fail(LB_ERR_UNSUPPORTED, "lb_read_bwd: shared memory does not fit for d=%d, n=%d", d, n);
 
     CUtensorMap tmV, tmG, tmDV, tmH0;
@@ -622,7 +642,7 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
         p.Gst = dV; p.Wt = sg.Wt; p.KQt = sg.KQt; p.Qall = sg.Qall; p.qrow_bytes = qrow; p.n_total = N;
         p.fin2 = sg.dv0 ? 1 : 0; p.dv0_out = sg.dv0; p.neg0_out = sg.dx0;
     }
-    int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms;
+    int cap = g_opt.grid_cap > 0 ? g_opt.grid_cap : di.sms * (ncw == 4 ? 2 : 1);
     if (cap > kMaxGrid) cap = kMaxGrid;
     const int grid = (int)(p.tok_tiles < cap ? p.tok_tiles : cap);
     cudaError_t e = lb::launch_read_bwd(dtype, fr, ncw, tmV, tmG, tmDV, tmH0, p, grid, st);

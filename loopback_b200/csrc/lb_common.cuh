@@ -255,6 +255,19 @@ template <> struct Store<float> {
     }
 };
 
+// acc += a.lo * b.lo (acc0) and a.hi * b.hi (acc1) for two packed bf16 pairs: the mixed-precision fma of sm_100
+// (bf16 x bf16 product, exact in fp32, added in fp32 with one rounding) -- the same values as unpacking both operands to
+// fp32 and an fp32 fma, without the unpacking
+__device__ __forceinline__ void fma_bf16x2(uint32_t a, uint32_t b, float &acc0, float &acc1) {
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\t"
+        "mov.b32 {al, ah}, %2;\n\t"
+        "mov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, al, bl, %0;\n\t"
+        "fma.rn.f32.bf16 %1, ah, bh, %1;\n\t}"
+        : "+f"(acc0), "+f"(acc1)
+        : "r"(a), "r"(b));
+}
+
 // streaming global accesses: read-once data bypasses L1, stores do not allocate in L1
 __device__ __forceinline__ uint4 ld_global_stream_v4(const void *p) {
     uint4 v;

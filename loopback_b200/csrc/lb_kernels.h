@@ -148,8 +148,8 @@ struct ReadBwdParams {
     void *Gst = nullptr;          // [N][n_tok][d]: the g row of every backward step (slice n-1 is written, slices n.. are read)
     float *Wt = nullptr;          // [N][N][n_tok]: entry [s][i] = step s's coefficient of g in the gradient of update i < s
     float *KQt = nullptr;         // ... and of the step's query q_s
-    const float *Qall = nullptr;  // [N-1][d] every query
-    int qrow_bytes = 0;           // d * 4: a query row travels with each g tile
+    const float *Qall = nullptr;  // [N-1][chunks * 512 / elem] every query, permuted by lb_permute_queries
+    int qrow_bytes = 0;           // bytes of such a row: a query row travels with each g tile
     int n_total = 0;              // N
     int fin2 = 0;                 // 1 (the step-1 backward): also finish update 0 into dv0_out / neg0_out
     void *dv0_out = nullptr, *neg0_out = nullptr;
@@ -159,6 +159,7 @@ size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec,
 cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, const CUtensorMap &tmG,
                             const CUtensorMap &tmDV, const CUtensorMap &tmH0, const ReadBwdParams &p, int grid,
                             cudaStream_t stream);
+cudaError_t launch_permute_queries(const float *Q, float *Qp, int nq, int d, int vec, int row_floats, cudaStream_t stream);
 cudaError_t launch_dq_reduce(const float *dq_part, int rows, float *dq, int d, float scale, cudaStream_t stream);
 
 }  // namespace lb

@@ -24,7 +24,9 @@
 
 namespace lb {
 
-constexpr int kBwdScalarWarps = 2;
+// scalar warps per CTA: 2, or 1 in the half-size CTA (4 consumer warps) of which two share an SM
+constexpr int bwd_scalar_warps(int ncw) { return ncw == 4 ? 1 : 2; }
+constexpr int bwd_ctas_per_sm(int ncw) { return ncw == 4 ? 2 : 1; }
 constexpr int kBwdMaxStages = 12;
 constexpr int kBwdTables = 6;     // P, R, GT, W, ZL, DRP
 constexpr int kBwdMaxNcw = 16;
@@ -64,7 +66,7 @@ size_t read_bwd_smem_bytes(int fr, int ncw, int wpt, int stages, int n, int vec,
 //   newest update from the upstream-gradient rows g and the per-source scalars that the backward steps before this one
 //   left behind (this step leaves its own), and hands it out as in MODE 1.
 template <typename T, int FR, int NCW, bool SOLO, int MODE>
-__global__ void __launch_bounds__((NCW + 1 + kBwdScalarWarps) * 32, 1)
+__global__ void __launch_bounds__((NCW + 1 + bwd_scalar_warps(NCW)) * 32, bwd_ctas_per_sm(NCW))
 read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
                 const __grid_constant__ CUtensorMap tmDV, const __grid_constant__ CUtensorMap tmH0, ReadBwdParams p) {
     using S = Store<T>;
@@ -75,6 +77,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
     constexpr uint32_t kStageBytes = FR * NCW * kChunkBytes;
     constexpr int kConsumerThreads = NCW * 32;
     constexpr bool STEP = MODE >= 1, DEFER = MODE == 2;
+    constexpr int kBwdScalarWarps = bwd_scalar_warps(NCW);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NS = p.stages, n = p.n, WPT = SOLO ? 1 : p.wpt, BT = NCW / WPT;
@@ -168,8 +171,9 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             const uint32_t gk = gdkq_a + t4;
             // ---- g tile -> registers (as fp32 pairs)
             // (the one-warp-per-token shapes keep g packed and unpack it where it is used, to leave room for 4 fragments
-            // per lane; unpacked it costs the 4-fragment shape 200 bytes of spills)
-            constexpr bool PACKG = SOLO;
+            // per lane; unpacked it costs the 4-fragment shape 200 bytes of spills. The deferred form uses g once per
+            // source only, in the dot product, which takes it packed: every shape keeps it packed there)
+            constexpr bool PACKG = SOLO || DEFER;
             float2 g2[PACKG ? 1 : FR][P];
             uint4 gpk[PACKG ? FR : 1];
             auto load_g = [&](int k, float2 (&gf)[P]) {          // g fragment k as fp32 pairs
@@ -257,15 +261,27 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     if (lane == 0) mbar_arrive(empty_a + 8u * st);
                     if (++st == NS) { st = 0; ph ^= 1u; }
                     float2 d2a = make_float2(0.f, 0.f), d2b = make_float2(0.f, 0.f);
+                    if constexpr (PACKG && S::kBytes == 2) {
+                        // both operands are packed bf16: the dot product straight from the packed registers (the same
+                        // four partial sums, in the same order, as the unpacked route below)
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) {
-                        float2 vf[P], gf[P];
-                        S::unpack2(raw[k], vf);
-                        load_g(k, gf);
+                        for (int k = 0; k < FR; ++k) {
+                            fma_bf16x2(gpk[k].x, raw[k].x, d2a.x, d2a.y);
+                            fma_bf16x2(gpk[k].y, raw[k].y, d2b.x, d2b.y);
+                            fma_bf16x2(gpk[k].z, raw[k].z, d2a.x, d2a.y);
+                            fma_bf16x2(gpk[k].w, raw[k].w, d2b.x, d2b.y);
+                        }
+                    } else {
 #pragma unroll
-                        for (int e = 0; e < P; e += 2) {
-                            d2a = __ffma2_rn(gf[e], vf[e], d2a);
-                            d2b = __ffma2_rn(gf[e + 1], vf[e + 1], d2b);
+                        for (int k = 0; k < FR; ++k) {
+                            float2 vf[P], gf[P];
+                            S::unpack2(raw[k], vf);
+                            load_g(k, gf);
+#pragma unroll
+                            for (int e = 0; e < P; e += 2) {
+                                d2a = __ffma2_rn(gf[e], vf[e], d2a);
+                                d2b = __ffma2_rn(gf[e + 1], vf[e + 1], d2b);
+                            }
                         }
                     }
                     dnew = warp_sum((d2a.x + d2b.x) + (d2a.y + d2b.y));
@@ -391,14 +407,14 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                         const float2 fw2 = make_float2(fw, fw), fkq2 = make_float2(fkq, fkq);
 #pragma unroll
                         for (int k = 0; k < FR; ++k) {
-                            const int col = (chunk0 + k) * BW + lane * VEC;
-                            const bool in_row = valid[k] && col < p.d;
                             float2 gf[P];
                             S::unpack2(valid[k] ? lds_v4(sb + foff[k]) : zero4, gf);
+                            // the query row arrives permuted (lb_permute_queries): per chunk, quarter e4 of every lane's
+                            // columns is contiguous over the lanes, so these 128-bit reads are conflict-free
+                            const uint32_t qa = sb + kStageBytes + (uint32_t)(chunk0 + k) * (uint32_t)(BW * 4) + 16u * lane;
 #pragma unroll
                             for (int e4 = 0; e4 < V4; ++e4) {
-                                const float4 q4 = in_row ? lds_f4(sb + kStageBytes + 4u * (uint32_t)col + 16u * e4)
-                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+                                const float4 q4 = valid[k] ? lds_f4(qa + 512u * e4) : make_float4(0.f, 0.f, 0.f, 0.f);
                                 acc[k][2 * e4] = __ffma2_rn(fkq2, make_float2(q4.x, q4.y), acc[k][2 * e4]);
                                 acc[k][2 * e4 + 1] = __ffma2_rn(fkq2, make_float2(q4.z, q4.w), acc[k][2 * e4 + 1]);
                             }
@@ -622,7 +638,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     if (DEFER && item >= v0 + n && item != v0 + n + J) gj = item - v0 - n - (item > v0 + n + J ? J + 1 : 0);
                     mbar_arrive_expect_tx(fb, (uint32_t)(nch * BT * kChunkBytes) + (gj >= 0 ? (uint32_t)p.qrow_bytes : 0u));
                     if (gj >= 0)        // the query of step n + gj (row n - 1 + gj) rides behind the tile
-                        bulk_load(sb + kStageBytes, p.Qall + (long long)(n - 1 + gj) * p.d, (uint32_t)p.qrow_bytes, fb);
+                        bulk_load(sb + kStageBytes, p.Qall + (long long)(n - 1 + gj) * (p.qrow_bytes / 4), (uint32_t)p.qrow_bytes, fb);
                     if (p.rank4) {
                         if (item == 0) tma_load_3d(sb, &tmG, fb, 0, 0, tok0);
                         else if (item < v0) tma_load_3d(sb, &tmH0, fb, 0, 0, tok0);
@@ -718,7 +734,7 @@ static cudaError_t launch_bwd(const CUtensorMap &tmV, const CUtensorMap &tmG, co
                                       MODE == 2 ? p.qrow_bytes : 0);
     cudaError_t e = cudaFuncSetAttribute(read_bwd_kernel<T, FR, NCW, SOLO, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    read_bwd_kernel<T, FR, NCW, SOLO, MODE><<<grid, (NCW + 1 + kBwdScalarWarps) * 32, smem, stream>>>(tmV, tmG, tmDV, tmH0, p);
+    read_bwd_kernel<T, FR, NCW, SOLO, MODE><<<grid, (NCW + 1 + bwd_scalar_warps(NCW)) * 32, smem, stream>>>(tmV, tmG, tmDV, tmH0, p);
     return cudaGetLastError();
 }
 
@@ -736,7 +752,8 @@ cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, 
     LB_BWD_CASE(TT, 1, 16, false) LB_BWD_CASE(TT, 2, 16, false) LB_BWD_CASE(TT, 1, 12, false)                   \
     LB_BWD_CASE(TT, 2, 12, false) LB_BWD_CASE(TT, 1, 8, false) LB_BWD_CASE(TT, 2, 8, false)                     \
     LB_BWD_CASE(TT, 3, 8, false) LB_BWD_CASE(TT, 4, 8, false) LB_BWD_CASE(TT, 1, 8, true) LB_BWD_CASE(TT, 2, 8, true) \
-    LB_BWD_CASE(TT, 3, 8, true) LB_BWD_CASE(TT, 4, 8, true)
+    LB_BWD_CASE(TT, 3, 8, true) LB_BWD_CASE(TT, 4, 8, true)                                                     \
+    LB_BWD_CASE(TT, 1, 4, true) LB_BWD_CASE(TT, 2, 4, true) LB_BWD_CASE(TT, 3, 4, true) LB_BWD_CASE(TT, 4, 4, true)
     if (dtype == LB_DTYPE_BF16) { LB_BWD_ALL(__nv_bfloat16) } else { LB_BWD_ALL(float) }
 #undef LB_BWD_ALL
 #undef LB_BWD_CASE
@@ -761,6 +778,28 @@ __global__ void __launch_bounds__(256) dq_reduce_kernel(const float *__restrict_
         for (int k = 0; k < 8; ++k) tsum += red[k][cx];
         dq[col] = tsum * scale;
     }
+}
+
+// Qp[j][chunk][e4][lane][0..3] = Q[j][chunk * BW + lane * VEC + 4 e4 + 0..3] (zero past d): the order in which the
+// lanes of the deferred backward read a query row from shared memory.
+__global__ void __launch_bounds__(256) permute_queries_kernel(const float *__restrict__ Q, float *__restrict__ Qp, int nq, int d,
+                                                              int vec, int row_floats) {
+    const int bw = 32 * vec, v4 = vec / 4;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < (long long)nq * row_floats;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int j = (int)(idx / row_floats), o = (int)(idx - (long long)j * row_floats);
+        const int chunk = o / bw, r = o - chunk * bw;          // r = (e4 * 32 + lane) * 4 + c
+        const int e4 = r / 128, lane = (r >> 2) & 31, c = r & 3;
+        const int col = chunk * bw + lane * vec + 4 * e4 + c;
+        Qp[idx] = (e4 < v4 && col < d) ? Q[(long long)j * d + col] : 0.f;
+    }
+}
+
+cudaError_t launch_permute_queries(const float *Q, float *Qp, int nq, int d, int vec, int row_floats, cudaStream_t stream) {
+    const long long total = (long long)nq * row_floats;
+    if (total == 0) return cudaSuccess;
+    permute_queries_kernel<<<(unsigned)((total + 255) / 256 < 1024 ? (total + 255) / 256 : 1024), 256, 0, stream>>>(Q, Qp, nq, d, vec, row_floats);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_dq_reduce(const float *dq_part, int rows, float *dq, int d, float scale, cudaStream_t stream) {

@@ -304,7 +304,7 @@ class DattnStack:
     are when the stack is built, i.e. for one forward pass."""
     __slots__ = ("V", "R", "dV", "dR", "n_steps", "n_tok", "d", "eps", "Q", "QT", "DOTS", "r_done", "_scratch",
                  "fuse_final", "_scale_done", "_neg", "_last_write", "_dq", "_dh0", "_first_step", "_first_blend",
-                 "d_done", "defer_writes", "_pending", "_small", "deferred_grads", "_da", "_G", "_Wt", "_KQt", "_dv0",
+                 "d_done", "defer_writes", "_pending", "_small", "deferred_grads", "_da", "_G", "_Wt", "_KQt", "_dv0", "_Qp",
                  "_n_step_nodes")
 
     def __init__(self, n_steps: int, shape, dtype, device, query=None, eps: float = 1e-6):
@@ -351,7 +351,7 @@ class DattnStack:
         # gradient of its own update from what the later steps left. Decided by the pass's first backward (_da).
         self.deferred_grads = True
         self._da = None
-        self._G = self._Wt = self._KQt = self._dv0 = None
+        self._G = self._Wt = self._KQt = self._dv0 = self._Qp = None
         self._n_step_nodes = 0
         if query is not None:
             self.Q = query.detach().float().contiguous()
@@ -715,6 +715,12 @@ class FusedStepStk(torch.autograd.Function):
                 stack._G = torch.empty_like(stack.V)
                 stack._Wt = torch.empty((N, N, n_tok), device=dev, dtype=torch.float32)
                 stack._KQt = torch.empty((N, N, n_tok), device=dev, dtype=torch.float32)
+                code = dtype_code(stack.V.dtype)
+                stack._Qp = torch.empty((N - 1, int(_lib.lib().lb_permuted_query_row_floats(d, code))), device=dev,
+                                        dtype=torch.float32)
+                with _on(dev):
+                    check(_lib.lib().lb_permute_queries(ptr(stack.Q), ptr(stack._Qp), N - 1, d, code, stream_ptr()),
+                          "permute queries")
             dv0 = dx0 = None
             if step == 1:                     # update 0 has no step of its own: this backward finishes it too
                 dv0 = torch.empty(ctx.shape, device=dev, dtype=stack.V.dtype)
@@ -725,7 +731,7 @@ class FusedStepStk(torch.autograd.Function):
             with _on(dev), _timed("read_bwd", n, units):
                 check(_lib.lib().lb_step_bwd_deferred(
                     ptr(stack.V), ptr(stack.R), ptr(stack._G), ptr(stack.dR), ptr(stack._Wt), ptr(stack._KQt), ptr(stack.Q),
-                    ptr(g), ptr(gt_c), ptr(tcp), ctx.lam, ptr(c0c), ptr(lg), ptr(lse), ptr(lse0), ptr(dtc),
+                    ptr(stack._Qp), ptr(g), ptr(gt_c), ptr(tcp), ctx.lam, ptr(c0c), ptr(lg), ptr(lse), ptr(lse0), ptr(dtc),
                     ptr(stack._dq[step - 1]), ptr(stack.scratch()), ptr(dh), ptr(dx), ptr(dh0), int(dh0_accum),
                     int(ctx.blend), ctx.beta, ptr(dv0), ptr(dx0), n_tok, d, N, n, int(first), dtype_code(stack.V.dtype),
                     stream_ptr()), "step backward (deferred)")

@@ -4,6 +4,7 @@
     python -m loopback_b200.microbench read_fwd --tokens 32768 --d 1024 --N 24 --n 12 [--blend]
     python -m loopback_b200.microbench read_bwd --tokens 32768 --d 1024 --N 24 --n 12 [--first] [--blend]
     python -m loopback_b200.microbench step_bwd --tokens 32768 --d 1024 --N 24 --n 12 [--first] [--blend]
+    python -m loopback_b200.microbench step_bwd_deferred --tokens 32768 --d 1024 --N 24 --n 12 [--blend]
     python -m loopback_b200.microbench step_fwd --tokens 64 --d 2048 --N 80 --n 40 --no-flush     (decode-sized)
 
 Prints the average launch time, the row traffic the launch makes by design (GB) and the bandwidth that gives.
@@ -22,7 +23,7 @@ from . import _lib as L
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["write", "read_fwd", "read_bwd", "step_bwd", "step_fwd"])
+    ap.add_argument("kernel", choices=["write", "read_fwd", "read_bwd", "step_bwd", "step_bwd_deferred", "step_fwd"])
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--d", type=int, default=1024)
     ap.add_argument("--N", type=int, default=24, help="updates of the pass (N - 1 queries)")
@@ -104,7 +105,22 @@ def main():
             accum = 0 if a.first else 1
             head = [L.ptr(V), L.ptr(R), L.ptr(dV), L.ptr(dR), L.ptr(Q[0]), L.ptr(up), L.ptr(gt), L.ptr(tcp), lam,
                     L.ptr(c0), L.ptr(lg), L.ptr(lse), L.ptr(lse0), L.ptr(dtc), L.ptr(dq), L.ptr(scratch)]
-            if a.kernel == "read_bwd":
+            if a.kernel == "step_bwd_deferred":
+                G = dV                                   # the stack of upstream-gradient rows
+                Wt = torch.randn(N, N, T, device=dev, generator=g) * 0.1
+                KQt = torch.randn(N, N, T, device=dev, generator=g) * 0.01
+                Qp = torch.empty(NQ, int(lib.lb_permuted_query_row_floats(d, code)), device=dev)
+                L.check(lib.lb_permute_queries(L.ptr(Q), L.ptr(Qp), NQ, d, code, st), "permute queries")
+                units = 2 + n + (N - n) + 2 + (2 if a.blend else 0)
+                label = f"backward step (deferred), {n} sources of {N}{', blend' if a.blend else ''}"
+
+                def launch():
+                    L.check(lib.lb_step_bwd_deferred(L.ptr(V), L.ptr(R), L.ptr(G), L.ptr(dR), L.ptr(Wt), L.ptr(KQt), L.ptr(Q),
+                                                     L.ptr(Qp), L.ptr(up), L.ptr(gt), L.ptr(tcp), lam, L.ptr(c0), L.ptr(lg), L.ptr(lse),
+                                                     L.ptr(lse0), L.ptr(dtc), L.ptr(dq), L.ptr(scratch), L.ptr(dh), L.ptr(dx),
+                                                     L.ptr(dh0) if a.blend else None, 1, int(a.blend), 0.75, None, None, T, d,
+                                                     N, n, int(a.first), code, st), "step backward (deferred)")
+            elif a.kernel == "read_bwd":
                 units = n + (2 * n if accum else n) + 2
                 label = f"backward read (finalising), {n} sources, {'accumulating' if accum else 'first'}"
 
