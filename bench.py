@@ -169,7 +169,7 @@ def run_reference_arm(args, w):
 # ------------------------------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum over the bytes by design of the captured launches (d=1024, bf16, 8192
 # tokens; the summaries under profiles/ give the commands). Traffic grows in proportion to the tokens of a launch.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"read_bwd": 0.937, "read_fwd": 1.004, "write": 0.845}
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"read_bwd": 0.99, "read_fwd": 1.004, "write": 0.845}
 
 
 class Pass:
@@ -547,7 +547,7 @@ def main():
                     "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE[dominant] * by / cnt
                                 if w["d"] == 1024 and w["dtype"] == "bf16" else None),
                     "traffic_source": "ncu dram bytes of an 8192-token capture of the same kernel and row size "
-                                      "(profiles/step_bwd_cfg2_8192tok.md, read_fwd_cfg2_8192tok.md, "
+                                      "(profiles/step_bwd_deferred_cfg2_8192tok.md, read_fwd_cfg2_8192tok.md, "
                                       "write_mma_cfg2_32768tok.md), scaled by tokens",
                     "bytes_per_launch_avg": by / cnt, "ms_per_launch_avg": sec * 1e3 / cnt,
                     "note": "bytes by design of the launches that ran: the deferred step backward reads V (n rows), the "
