@@ -303,7 +303,6 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     sacc = fmaf(pj, gp, sacc);
                     const float b = pj * rj, a = b * gp;
                     const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
-#ifndef LB_EXP_NOAB
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
                         float2 vf[P];
@@ -311,14 +310,9 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
 #pragma unroll
                         for (int e = 0; e < P; ++e) {
                             A[k][e] = __ffma2_rn(a2, vf[e], A[k][e]);
-#ifndef LB_EXP_NOB
                             B[k][e] = __ffma2_rn(b2, vf[e], B[k][e]);
-#endif
                         }
                     }
-#else
-                    A[0][0].x += a2.x; B[0][0].x += b2.x;
-#endif
                 }
                 if (WPT > 1) named_bar_sync(bar_id, bar_threads);
                 if (i < n + DEPTH - 1) {          // after the loop v2 (SOLO: v1) still holds source n - 1 (used by phase 2)
