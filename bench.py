@@ -242,6 +242,26 @@ class Runner:
             self.dist.barrier()
         self.torch.cuda.synchronize()
 
+    def exchange(self, cell):
+        """The pass's only exchange: the (N-1) x d query gradient summed over the ranks. With the peer reduction enabled
+        on the cell, the pass's last backward has already done it (inside the captured graph too)."""
+        if self.world > 1 and getattr(cell, "peer_reduce", None) is None:
+            self.dist.all_reduce(cell.query.grad)
+
+    def enable_peer(self, cell, mode):
+        """Turn on the peer-memory reduction of the query gradient on every rank, or on none. Returns what is in use."""
+        if self.world == 1 or mode != "peer":
+            return "none" if self.world == 1 else "nccl all-reduce"
+        try:
+            cell.enable_peer_reduce(self.dev)
+            ok, why = True, ""
+        except Exception as e:  # noqa: BLE001 -- reported in the JSON line; the NCCL all-reduce takes over
+            ok, why = False, f"{type(e).__name__}: {e}"[:160]
+        if self.all_agree(ok):
+            return "peer memory, one-shot (lb_peer_allreduce) as the last backward's epilogue"
+        cell.__dict__["peer_reduce"] = None
+        return "nccl all-reduce (peer memory unavailable" + (": " + why if why else " on another rank") + ")"
+
     def timed(self, fn, steps):
         torch = self.torch
         self.barrier()
@@ -287,8 +307,8 @@ class Runner:
 
         def eager_pass():
             P.run()
-            if backward and world > 1:
-                dist.all_reduce(P.cell.query.grad)           # the (N-1) x d query gradient: the only exchange
+            if backward:
+                self.exchange(P.cell)                        # the (N-1) x d query gradient: the only exchange
         for _ in range(warmup):
             eager_pass()
         win = sampler.window() if sampler is not None else ClockSampler._Window()
@@ -300,8 +320,8 @@ class Runner:
             if self.all_agree(g is not None):
                 def graph_pass():
                     g.replay()
-                    if backward and world > 1:
-                        dist.all_reduce(P.cell.query.grad)
+                    if backward:
+                        self.exchange(P.cell)
                 for _ in range(3):
                     graph_pass()
                 win_g = sampler.window() if sampler is not None else ClockSampler._Window()
@@ -384,6 +404,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (no other configurations, no reference legs)")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on small cases)")
     ap.add_argument("--opt", action="append", default=[], help="library tuning knob name=value (lb_set_option)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the query gradient is summed over the ranks (peer memory one-shot, or NCCL)")
     ap.add_argument("--no-graph", action="store_true", help="do not replay the pass as a CUDA graph for `value`")
     ap.add_argument("--path", default="fused", choices=["fused", "fused_combine", "dropin"],
                     help="how the headline pass calls the read (A/B): one node per step, prologue in the kernels, "
@@ -425,9 +447,15 @@ def main():
     row = d * elem
     P = Pass(w, dev, seed=rank)
 
+    peers = {}                                   # cell -> its PeerQueryGrad (only the one-node-per-step path uses it)
+
     def set_path(cell, path):
         cell.fuse_prologue = path in ("fused", "fused_combine")
         cell.fuse_step = path == "fused"
+        if cell.peer_reduce is not None:
+            peers[id(cell)] = cell.peer_reduce
+        cell.__dict__["peer_reduce"] = peers.get(id(cell)) if path == "fused" else None
+    exchange = R.enable_peer(P.cell, args.exchange) if w["backward"] else "none"
     set_path(P.cell, args.path)
 
     # ---- device-resident timing, with per-launch events on the dominant kernels -------------------------------
@@ -448,8 +476,8 @@ def main():
 
     def one_pass():
         P.run()
-        if w["backward"] and world > 1:
-            dist.all_reduce(P.cell.query.grad)
+        if w["backward"]:
+            R.exchange(P.cell)
     for _ in range(args.warmup):
         one_pass()
     FD.LAUNCH_TIMER = Timer
@@ -473,8 +501,8 @@ def main():
         if R.all_agree(graph is not None):
             def graph_pass():
                 graph.replay()
-                if w["backward"] and world > 1:
-                    dist.all_reduce(P.cell.query.grad)
+                if w["backward"]:
+                    R.exchange(P.cell)
             for _ in range(3):
                 graph_pass()
             assert FD.device_error() == 0
@@ -569,6 +597,21 @@ def main():
     elif not args.no_e2e:
         e2e = e2e_leg(R, P, w, args)
 
+    # ---- the exchange alone, both ways (N > 1): the (N-1) x d query gradient summed over the ranks ----------------
+    exchange_us = None
+    if world > 1 and w["backward"]:
+        qg = torch.randn(N - 1, d, device=dev)
+        for _ in range(5):
+            dist.all_reduce(qg)
+        exchange_us = {"nccl_all_reduce": R.timed(lambda: dist.all_reduce(qg), 50) / 50 * 1e3}
+        pr = peers.get(id(P.cell)) or P.cell.peer_reduce
+        if pr is not None:
+            for _ in range(5):
+                pr.reduce()
+            exchange_us["peer_memory_one_shot"] = R.timed(pr.reduce, 50) / 50 * 1e3
+        exchange_us["what"] = "back-to-back eager calls, device time per call, max over ranks"
+        assert FD.device_error() == 0
+
     # ---- the other BASELINE configurations ------------------------------------------------------------------------
     sharded, depth_sweep, triton_leg, torch_leg = None, None, None, None
     if not args.no_extras:
@@ -581,6 +624,7 @@ def main():
             total = ws["b"] * ws["t"]
             per = total // world
             Ps = Pass(ws, dev, seed=rank, n_tok=per)
+            R.enable_peer(Ps.cell, args.exchange)
             set_path(Ps.cell, args.path)
             # a graph keeps a second copy of the pass's memory alive: only where that fits comfortably
             use_graph = not args.no_graph and per * ws["d"] * 2 * 24 * 8 < 60 * 2**30
@@ -625,6 +669,7 @@ def main():
                                    f"{'forward+backward' if w['backward'] else 'forward only'}",
                        "storage_dtype": w["dtype"], "tokens_per_gpu": n_tok, "l2": l2_note,
                        "parallelism": f"tokens x{world}" if world > 1 else "single GPU",
+                       "query_grad_exchange": exchange, "query_grad_exchange_us": exchange_us,
                        "path": args.path, "launch": launch_mode, "eager_ms_per_step": eager_ms_per_step,
                        "pass_algorithmic_units_per_token": pass_units,
                        "pass_algorithmic_gbs": pass_gbs, "pass_frac_of_peak": pass_gbs / peak,
@@ -753,8 +798,8 @@ def e2e_leg(R, P, w, args):
             if w["backward"]:
                 stage_grads()
                 torch.autograd.backward(outs, [gbufs[s] for s in range(N)])
-        if w["backward"] and world > 1:
-            dist.all_reduce(cell.query.grad)
+        if w["backward"]:
+            R.exchange(cell)
         out_host.copy_(x.detach(), non_blocking=True)
         if w["backward"]:
             dq_host.copy_(cell.query.grad, non_blocking=True)

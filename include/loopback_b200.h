@@ -230,6 +230,30 @@ int lb_read_bwd_noalloc(const void *V, const float *R, void *dV, float *dR, cons
                         const float *LSE0, float *dcbar, float *dq, int64_t n_tok, int d, int N, int n, int accum,
                         int dtype, void *stream);
 
+/* The most ranks lb_peer_allreduce serves (the GPUs of one NVLink node). */
+#define LB_MAX_PEERS 16
+
+/* 32-bit words of the flag block every rank provides to lb_peer_allreduce (zeroed once, before the first call of any
+ * rank; never touched by the host afterwards). */
+int lb_peer_flag_words(void);
+
+/* One-shot all-reduce (fp32 sum) of the query gradient over the GPUs of one node through peer memory: the pass's
+ * last backward leaves each rank's (N - 1, d) gradient in bufs[rank]; this one small launch per rank then sums all
+ * ranks' buffers in rank order (every rank gets the same bits) into `out`.
+ *   bufs, flags  HOST arrays of `world` DEVICE pointers, rank-ordered: every rank's gradient buffer (n floats) and
+ *                flag block (lb_peer_flag_words() words), addressable from this GPU (peer-mapped: CUDA IPC or
+ *                symmetric memory); bufs[rank] / flags[rank] are this rank's own
+ *   out          [n] local result; n a multiple of 4; all ranks pass the same n
+ * The ranks' kernels wait on one another (plain flag words, ld.acquire.sys / st.release.sys; no multicast), so each
+ * rank needs a GPU of its own. Every wait is bounded by the "wait_cycles" option: a rank whose peer does not arrive
+ * records error 6 in the device error word (lb_device_error), skips its sum and returns. When the launch has
+ * completed, no peer reads bufs[rank] any more: the next pass may overwrite it. The call counter lives in the flag
+ * block, so the launch can be captured in a CUDA graph and replayed.
+ * Replaces the reduce-scatter FSDP issues for query.grad (trainer/flame/models/parallelize_fla.py:549-554) and the
+ * NCCL all-reduce of loopback_b200.dist.allreduce_query_grad. */
+int lb_peer_allreduce(const float *const *bufs, unsigned int *const *flags, int rank, int world, float *out, int64_t n,
+                      void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,6 +16,7 @@ LIB_PATH = os.environ.get("LOOPBACK_B200_LIB") or os.path.join(_HERE, "libloopba
 LB_DTYPE_F32 = 0
 LB_DTYPE_BF16 = 1
 LB_MAX_SOURCES = 128
+LB_MAX_PEERS = 16
 
 # every symbol include/loopback_b200.h declares: (name, restype, argtypes)
 _vp, _i, _i64, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
@@ -48,6 +49,8 @@ SYMBOLS = {
     "lb_permute_queries": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "lb_step_bwd_deferred": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                   _vp, _vp, _i, _i, _f, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp]),
+    "lb_peer_flag_words": (_i, []),
+    "lb_peer_allreduce": (_i, [_vp, _vp, _i, _i, _vp, _i64, _vp]),
     "lb_read_bwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
                                  _i, _i, _vp]),
 }

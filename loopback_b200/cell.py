@@ -34,7 +34,16 @@ class LoopDeltaAttnRes(nn.Module):
         self.fuse_prologue = True      # fold the boundary blend and the coefficient append/decay into the kernels
         self.fuse_step = True          # ... and make the write and the read of a step one autograd node
         self.deferred_grads = True     # ... whose backward keeps no gradient stack (DattnStack.deferred_grads)
+        self.__dict__["peer_reduce"] = None   # see enable_peer_reduce (not a submodule, not part of the state dict)
         self.reset_parameters()
+
+    def enable_peer_reduce(self, device, group=None):
+        """Data parallel over the GPUs of one NVLink node: from now on the pass's last backward sums the query gradient
+        over the ranks of `group` itself, through peer memory (dist.PeerQueryGrad), and `query.grad` arrives summed;
+        the caller (or its data-parallel wrapper) must not reduce it again. Collective: every rank calls it once."""
+        from .dist import PeerQueryGrad
+        self.__dict__["peer_reduce"] = PeerQueryGrad((self.num_steps - 1, self.dim), device, group)
+        return self.peer_reduce
 
     def reset_parameters(self):
         with torch.no_grad():
@@ -78,6 +87,7 @@ class LoopDeltaAttnRes(nn.Module):
                               eps=self.eps)
         stack.defer_writes = bool(fuse_decode and scores)
         stack.deferred_grads = bool(self.deferred_grads)
+        stack.peer_reduce = self.peer_reduce
         return stack
 
     def combine(self, proposal, h0, deltas, coeffs, prior_coeffs, loop_idx, block_idx, keys=None, stack=None):

@@ -539,6 +539,31 @@ int lb_permute_queries(const float *Q, float *Qp, int NQ, int d, int dtype, void
     return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_permute_queries launch");
 }
 
+int lb_peer_flag_words(void) { return lb::kPeerFlagWords; }
+
+int lb_peer_allreduce(const float *const *bufs, unsigned int *const *flags, int rank, int world, float *out, int64_t n,
+                      void *stream) {
+    if (!bufs || !flags || !out) return fail(LB_ERR_ARG, "lb_peer_allreduce: NULL pointer");
+    if (world < 1 || world > lb::kMaxPeers || rank < 0 || rank >= world)
+        return fail(LB_ERR_ARG, "lb_peer_allreduce: needs 1 <= world <= LB_MAX_PEERS and 0 <= rank < world");
+    if (n < 0 || n % 4) return fail(LB_ERR_ARG, "lb_peer_allreduce: n must be a non-negative multiple of 4 floats");
+    if (n == 0) return LB_OK;
+    lb::PeerReduceParams p{};
+    for (int r = 0; r < world; ++r) {
+        if (!bufs[r] || !flags[r]) return fail(LB_ERR_ARG, "lb_peer_allreduce: NULL peer pointer");
+        if (!aligned16(bufs[r]) || ((uintptr_t)flags[r] & 3u)) return fail(LB_ERR_ALIGN, "lb_peer_allreduce: buffers must be 16-byte aligned");
+        p.bufs[r] = bufs[r]; p.flags[r] = flags[r];
+    }
+    if (!aligned16(out)) return fail(LB_ERR_ALIGN, "lb_peer_allreduce: out must be 16-byte aligned");
+    DeviceInfo di;
+    int rc;
+    if ((rc = device_info(&di))) return rc;
+    p.out = out; p.n4 = n / 4; p.rank = rank; p.world = world;
+    p.wait_cycles = wait_limit(); p.err_word = di.err_word;
+    cudaError_t e = lb::launch_peer_allreduce(p, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? LB_OK : cuda_fail(e, "lb_peer_allreduce launch");
+}
+
 int lb_step_bwd_deferred(const void *V, const float *R, void *G, float *dR, float *Wt, float *KQt, const float *Q,
                          const float *Qp, const void *g, const float *gt, const float *tc_prev, float lam, const float *c0, const float *LG,
                          const float *LSE, const float *LSE0, float *dtc_prev, float *dq, void *scratch, void *dh, void *dx,

@@ -28,6 +28,7 @@ enum DeviceError : int {
     kDevWaitScalars = 3,   // a consumer gave up waiting for the scalar tables of a tile
     kDevWaitScalarSlot = 4,
     kDevWaitDrain = 5,     // the producer gave up waiting for its own copies in flight at exit
+    kDevWaitPeer = 6,      // the peer all-reduce gave up waiting for another rank's flag
 };
 
 // The error word itself is a __device__ int owned by lb_api.cu (one per device); kernels get its address.

@@ -162,4 +162,22 @@ cudaError_t launch_read_bwd(int dtype, int fr, int ncw, const CUtensorMap &tmV, 
 cudaError_t launch_permute_queries(const float *Q, float *Qp, int nq, int d, int vec, int row_floats, cudaStream_t stream);
 cudaError_t launch_dq_reduce(const float *dq_part, int rows, float *dq, int d, float scale, cudaStream_t stream);
 
+// The one-shot all-reduce of the query gradient through peer memory (lb_peer_allreduce)
+constexpr int kMaxPeers = 16;      // ranks of a node
+constexpr int kPeerCtas = 32;      // CTAs (= slices of the buffer) at most
+// a rank's flag block, in 32-bit words: [2 phases][kMaxPeers source ranks][kPeerCtas], then the CTAs' call counters
+constexpr int kPeerFlagWords = 2 * kMaxPeers * kPeerCtas + kPeerCtas;
+struct PeerReduceParams {
+    const float *bufs[kMaxPeers];  // every rank's buffer, rank-ordered (bufs[rank] is this rank's own)
+    unsigned *flags[kMaxPeers];    // every rank's flag block
+    float *out;                    // [4 n4] the sum
+    long long n4;                  // 16-byte groups of the buffer
+    long long slice4;              // groups per CTA (filled in by the launcher)
+    int rank, world;
+    long long wait_cycles;
+    int *err_word;
+};
+int peer_allreduce_ctas(long long n4);
+cudaError_t launch_peer_allreduce(PeerReduceParams p, cudaStream_t stream);
+
 }  // namespace lb

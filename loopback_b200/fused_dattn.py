@@ -305,7 +305,7 @@ class DattnStack:
     __slots__ = ("V", "R", "dV", "dR", "n_steps", "n_tok", "d", "eps", "Q", "QT", "DOTS", "r_done", "_scratch",
                  "fuse_final", "_scale_done", "_neg", "_last_write", "_dq", "_dh0", "_first_step", "_first_blend",
                  "d_done", "defer_writes", "_pending", "_small", "deferred_grads", "_da", "_G", "_Wt", "_KQt", "_dv0", "_Qp",
-                 "_n_step_nodes")
+                 "_n_step_nodes", "peer_reduce")
 
     def __init__(self, n_steps: int, shape, dtype, device, query=None, eps: float = 1e-6):
         b, t, d = shape
@@ -353,6 +353,9 @@ class DattnStack:
         self._da = None
         self._G = self._Wt = self._KQt = self._dv0 = self._Qp = None
         self._n_step_nodes = 0
+        # a dist.PeerQueryGrad: the step nodes then write their query-gradient rows into its peer-addressable buffer and
+        # the pass's last backward returns the sum over the ranks (no collective is left to the caller)
+        self.peer_reduce = None
         if query is not None:
             self.Q = query.detach().float().contiguous()
             self.DOTS = torch.empty((max(1, self.Q.shape[0]), self.n_steps, b * t), dtype=torch.float32, device=device)
@@ -697,7 +700,12 @@ class FusedStepStk(torch.autograd.Function):
         g = g.contiguous()
         gt_c = None if gt is None else gt.reshape(n_tok, n).float().contiguous()
         if stack._dq is None:
-            stack._dq = torch.zeros((ctx.q_rows, d), device=dev, dtype=torch.float32)
+            if stack.peer_reduce is not None:
+                if stack.peer_reduce.shape != (ctx.q_rows, d):
+                    raise RuntimeError("delta_attnres stacked read: the peer reduction was built for another query shape")
+                stack._dq = stack.peer_reduce.rows.zero_()
+            else:
+                stack._dq = torch.zeros((ctx.q_rows, d), device=dev, dtype=torch.float32)
         dh0, dh0_accum = None, False
         if ctx.want_dh0:
             dh0_accum = stack._dh0 is not None
@@ -748,7 +756,10 @@ class FusedStepStk(torch.autograd.Function):
                                              int(bool(accum)), dtype_code(stack.V.dtype), stream_ptr()), "step backward")
         dquery = dh0_out = None
         if step == stack._first_step:             # the earliest step runs last: the pass's query gradient is complete
-            dquery, stack._dq = stack._dq.to(ctx.q_dtype), None
+            if stack.peer_reduce is not None:     # ... and is summed over the ranks here, through peer memory
+                dquery, stack._dq = stack.peer_reduce.reduce().to(ctx.q_dtype), None
+            else:
+                dquery, stack._dq = stack._dq.to(ctx.q_dtype), None
         if ctx.want_dh0 and step == stack._first_blend:
             dh0_out, stack._dh0 = stack._dh0, None
         first = ()

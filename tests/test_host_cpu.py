@@ -79,6 +79,29 @@ def test_shard_tokens():
         shard_tokens(8, 2, 2)
 
 
+def test_peer_allocation_layout():
+    """A rank's peer-addressable allocation: the gradient padded to whole 16-byte groups, then the flag block on a
+    256-byte boundary; the flag block's size comes from the library (no GPU needed to ask)."""
+    from loopback_b200.dist import peer_slices
+    from loopback_b200 import _lib
+    words = int(_lib.lib().lb_peer_flag_words())
+    assert words == 2 * _lib.LB_MAX_PEERS * 32 + 32
+    for n in (0, 1, 4, 23 * 1024, 79 * 2048 + 2):
+        grad, off, total = peer_slices(n, words)
+        assert grad % 4 == 0 and 0 <= grad - n < 4
+        assert off % 64 == 0 and off >= grad and total == off + words
+    with pytest.raises(ValueError):
+        peer_slices(-1, words)
+
+
+def test_peer_reduce_needs_a_process_group():
+    from loopback_b200.cell import LoopDeltaAttnRes
+    cell = LoopDeltaAttnRes(64, 2, 2)
+    assert cell.peer_reduce is None and "peer_reduce" not in cell.state_dict()
+    with pytest.raises(RuntimeError):
+        cell.enable_peer_reduce("cuda")
+
+
 WORKER = r"""
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])
