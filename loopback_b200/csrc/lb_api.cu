@@ -618,11 +618,13 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
     static const int kNcw[3] = {12, 16, 8}, kFrMax[3] = {2, 2, 4};
     if (nch <= 4 && g_opt.bwd_wpt <= 1 && (g_opt.bwd_warps == 0 || g_opt.bwd_warps == 8 || g_opt.bwd_warps == 4)) {
         // 8 consumer warps and one CTA per SM, or ("bwd_warps" = 4) half-size CTAs of 4 consumer warps, two per SM:
-        // two independent pipelines whose phases drift apart
-        // (default: the half-size CTAs for the deferred form's launches that are mostly phase 1, n >= 2N/3: +8 % there,
-        // -3 % where phase 2 dominates)
-        const bool half = g_opt.bwd_warps == 4 || (g_opt.bwd_warps == 0 && sg.deferred && 3 * n >= 2 * N);
+        // two independent pipelines whose phases drift apart (no faster since phase 1 became straight-line code: an option only)
+        const bool half = g_opt.bwd_warps == 4;
         ncw = half ? 4 : 8; wpt = 1; fr = nch;
+    } else if (sg.deferred && !g_opt.bwd_warps && !g_opt.bwd_wpt && nch % 3 == 0 && (nch == 6 || nch == 12 || nch == 24)) {
+        // the deferred form keeps g packed and has registers for 3 fragments per warp: 8 consumer warps, fewer warps
+        // per token to exchange partial dot products between (measured: -1 % at 6 chunks, -6 % at 12)
+        ncw = 8; fr = 3; wpt = nch / 3;
     } else {
         for (int a = 0; a < 3; ++a) {
             if (g_opt.bwd_warps && g_opt.bwd_warps != kNcw[a]) continue;

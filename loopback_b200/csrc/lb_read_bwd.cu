@@ -22,6 +22,10 @@
 #include "lb_common.cuh"
 #include "lb_kernels.h"
 
+#ifndef LB_BWD_UNROLL
+#define LB_BWD_UNROLL 4
+#endif
+
 namespace lb {
 
 // scalar warps per CTA: 2, or 1 in the half-size CTA (4 consumer warps) of which two share an SM
@@ -248,11 +252,17 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             }
             float sacc = 0.f, d1 = 0.f, d2 = 0.f;  // this warp's g . v of sources i-1 and i-2
             constexpr int DEPTH = SOLO ? 1 : 2;
-            for (int i = 0; i < n + DEPTH; ++i) {
+            // One iteration, specialised at compile time on whether it still loads a source (LOAD: i < n) and whether a
+            // source is ready to be accumulated (ACC: i >= DEPTH), so that the steady-state body is straight-line code:
+            // the accumulation of the older source is independent of the new source's dot product and shuffle
+            // reduction, and the five dependent shuffle steps are written between its fragments so that their latency
+            // is covered by its FMAs instead of stalling the warp.
+            auto iter = [&](int i, auto load_tag, auto acc_tag) {
+                constexpr bool LOAD = decltype(load_tag)::value, ACC = decltype(acc_tag)::value;
                 if (WPT > 1 && i >= 1 && i <= n && lane == 0) sts_f32(xch_a + 4u * (((i - 1) & 1) * kBwdMaxNcw + warp), d1);
                 uint4 raw[FR];
-                float dnew = 0.f;
-                if (i < n) {
+                float x = 0.f;                    // this lane's share of g . v_i, then the warp's
+                if constexpr (LOAD) {
                     if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
                     const uint32_t sb = stages_a + (uint32_t)st * pitch;
 #pragma unroll
@@ -260,6 +270,27 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty_a + 8u * st);
                     if (++st == NS) { st = 0; ph ^= 1u; }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < FR; ++k) raw[k] = zero4;
+                }
+                float2 a2 = make_float2(0.f, 0.f), b2 = a2;
+                if constexpr (ACC) {
+                    const uint32_t j4 = (uint32_t)(i - DEPTH) * BT4;
+                    float gd = SOLO ? d1 : d2;
+                    if (WPT > 1) {
+                        gd = 0.f;
+                        const uint32_t xa = xch_a + 4u * (((i - 2) & 1) * kBwdMaxNcw + t * WPT);
+                        for (int w2 = 0; w2 < WPT; ++w2) gd += lds_f32(xa + 4u * w2);
+                    }
+                    if (part == 0 && lane == 0) sts_f32(gk + j4, gd);
+                    const float pj = lds_f32(tb + j4), rj = lds_f32(tb + tfl4 + j4);
+                    const float gp = mass * (gd + lds_f32(tb + 2u * tfl4 + j4));
+                    sacc = fmaf(pj, gp, sacc);
+                    const float b = pj * rj, a = b * gp;
+                    a2 = make_float2(a, a); b2 = make_float2(b, b);
+                }
+                if constexpr (LOAD) {
                     float2 d2a = make_float2(0.f, 0.f), d2b = make_float2(0.f, 0.f);
                     if constexpr (PACKG && S::kBytes == 2) {
                         // both operands are packed bf16: the dot product straight from the packed registers (the same
@@ -284,42 +315,46 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                             }
                         }
                     }
-                    dnew = warp_sum((d2a.x + d2b.x) + (d2a.y + d2b.y));
-                } else {
-#pragma unroll
-                    for (int k = 0; k < FR; ++k) raw[k] = zero4;
+                    x = (d2a.x + d2b.x) + (d2a.y + d2b.y);
                 }
-                if (i >= DEPTH) {
-                    const uint32_t j4 = (uint32_t)(i - DEPTH) * BT4;
-                    float gd = SOLO ? d1 : d2;
-                    if (WPT > 1) {
-                        gd = 0.f;
-                        const uint32_t xa = xch_a + 4u * (((i - 2) & 1) * kBwdMaxNcw + t * WPT);
-                        for (int w2 = 0; w2 < WPT; ++w2) gd += lds_f32(xa + 4u * w2);
+                // the warp reduction (offsets 16, 8, 4, 2, 1: warp_sum's order) with the accumulation spread between its steps
+                constexpr int kShuffles = 5;
+#pragma unroll
+                for (int k = 0; k < (FR > kShuffles ? FR : kShuffles); ++k) {
+                    if constexpr (LOAD) {
+                        if (k < kShuffles) x += __shfl_xor_sync(0xffffffffu, x, 16 >> k);
                     }
-                    if (part == 0 && lane == 0) sts_f32(gk + j4, gd);
-                    const float pj = lds_f32(tb + j4), rj = lds_f32(tb + tfl4 + j4);
-                    const float gp = mass * (gd + lds_f32(tb + 2u * tfl4 + j4));
-                    sacc = fmaf(pj, gp, sacc);
-                    const float b = pj * rj, a = b * gp;
-                    const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
+                    if constexpr (ACC) {
+                        if (k < FR) {
+                            float2 vf[P];
+                            S::unpack2(SOLO ? v1[k] : v2[k], vf);
 #pragma unroll
-                    for (int k = 0; k < FR; ++k) {
-                        float2 vf[P];
-                        S::unpack2(SOLO ? v1[k] : v2[k], vf);
-#pragma unroll
-                        for (int e = 0; e < P; ++e) {
-                            A[k][e] = __ffma2_rn(a2, vf[e], A[k][e]);
-                            B[k][e] = __ffma2_rn(b2, vf[e], B[k][e]);
+                            for (int e = 0; e < P; ++e) {
+                                A[k][e] = __ffma2_rn(a2, vf[e], A[k][e]);
+                                B[k][e] = __ffma2_rn(b2, vf[e], B[k][e]);
+                            }
                         }
                     }
                 }
                 if (WPT > 1) named_bar_sync(bar_id, bar_threads);
                 if (i < n + DEPTH - 1) {          // after the loop v2 (SOLO: v1) still holds source n - 1 (used by phase 2)
-                    d2 = d1; d1 = dnew;
+                    d2 = d1; d1 = x;
 #pragma unroll
                     for (int k = 0; k < FR; ++k) { if constexpr (!SOLO) v2[k] = v1[k]; v1[k] = raw[k]; }
                 }
+            };
+            {
+                int i = 0;
+                for (; i < DEPTH; ++i) {                                   // fill: nothing to accumulate yet
+                    if (i < n) iter(i, std::true_type{}, std::false_type{});
+                    else iter(i, std::false_type{}, std::false_type{});
+                }
+                // (unrolled in the deferred form: the register rotation at the end of an iteration disappears into the
+                // renaming between the copies; the other forms have no registers to spare for it)
+                constexpr int kUnroll = DEFER ? LB_BWD_UNROLL : 1;
+#pragma unroll kUnroll
+                for (; i < n; ++i) iter(i, std::true_type{}, std::true_type{});      // steady state
+                for (; i < n + DEPTH; ++i) iter(i, std::false_type{}, std::true_type{});   // drain
             }
             // ---- query-gradient partial of this thread's columns: private shared-memory slots
             if (alive && tok_in) {
