@@ -18,6 +18,8 @@
 //     they are (no ldmatrix, nothing written back to shared memory); accumulators stay in registers across the whole
 //     row. No CTA-wide barrier.
 // Waits are bounded (lb_common.cuh); a CTA that gives up unwinds and reports through the device error word.
+#include <type_traits>
+
 #include "lb_common.cuh"
 #include "lb_kernels.h"
 
@@ -126,7 +128,11 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                 if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
                 if (NT > 0 && alive && !mbar_wait(qfull_a + 8u * qb, qph, wc, kDevWaitScalars)) alive = false;
                 const uint32_t sh = stages_a + (uint32_t)st * stage_bytes, sx = sh + tile_bytes;
-                if (active && alive) {
+                // The chunk's work, specialised at compile time on the number of query terms (a chunk whose queries are
+                // exact in bf16, e.g. a bf16 parameter, has zero mid and lo terms), so that its loads, subtractions,
+                // stores and mma steps are one straight-line block the scheduler can interleave freely.
+                auto chunk_body = [&](auto terms_tag) {
+                    constexpr int terms = decltype(terms_tag)::value;
                     // Both mma operands come straight from 16-byte shared-memory reads: lane (g, t4) owns fragment
                     // t4 of a 32-column group for rows g and g + 8 of each 16-token tile. Its 8 columns feed two mma
                     // steps (columns 0-3, then 4-7, as the k pairs {2 t4, 2 t4 + 1} and {2 t4 + 8, 2 t4 + 9}); the
@@ -145,9 +151,6 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                             for (int e = 0; e < 4; ++e) part[mi][nt][e] = 0.f;
                     }
                     const uint32_t qbase = qs_a + (uint32_t)qb * 3u * kQTerm;
-                    // a chunk whose queries are exact in bf16 (e.g. a bf16 parameter) has zero mid and lo terms
-                    const int terms = NT > 0 ? ((lds_volatile_s32(qlow_a + 8u * qb) | lds_volatile_s32(qlow_a + 8u * qb + 4u)) ? 3 : 1)
-                                             : 0;
 #pragma unroll
                     for (int grp = 0; grp < kWmKC / 32; ++grp) {
                         const uint32_t unit = (uint32_t)(((4 * grp + t4) ^ g) << 4);      // swizzled; row & 7 == g
@@ -181,17 +184,15 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
                         }
                         if (NT > 0) {
 #pragma unroll
-                            for (int sp = 2; sp >= 0; --sp) {          // small terms first
-                                if (sp < terms) {
+                            for (int sp = terms - 1; sp >= 0; --sp) {          // small terms first
 #pragma unroll
-                                    for (int nt = 0; nt < NT; ++nt) {
-                                        const uint4 b = lds_v4(qbase + sp * kQTerm + (uint32_t)(8 * nt + g) * kWmRow + unit);
-                                        const uint32_t b0[2] = {b.x, b.y}, b1[2] = {b.z, b.w};
+                                for (int nt = 0; nt < NT; ++nt) {
+                                    const uint4 b = lds_v4(qbase + sp * kQTerm + (uint32_t)(8 * nt + g) * kWmRow + unit);
+                                    const uint32_t b0[2] = {b.x, b.y}, b1[2] = {b.z, b.w};
 #pragma unroll
-                                        for (int mi = 0; mi < MT; ++mi) {
-                                            mma_bf16(part[mi][nt], afr[0][mi], b0);
-                                            mma_bf16(part[mi][nt], afr[1][mi], b1);
-                                        }
+                                    for (int mi = 0; mi < MT; ++mi) {
+                                        mma_bf16(part[mi][nt], afr[0][mi], b0);
+                                        mma_bf16(part[mi][nt], afr[1][mi], b1);
                                     }
                                 }
                             }
@@ -211,6 +212,12 @@ write_mma_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant_
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) acc[mi][nt][e] += part[mi][nt][e];
                     }
+                };
+                if (active && alive) {
+                    if (NT > 0 && (lds_volatile_s32(qlow_a + 8u * qb) | lds_volatile_s32(qlow_a + 8u * qb + 4u)) != 0)
+                        chunk_body(std::integral_constant<int, 3>{});
+                    else
+                        chunk_body(std::integral_constant<int, (NT > 0 ? 1 : 0)>{});
                 }
                 __syncwarp();
                 if (lane == 0) {
