@@ -621,9 +621,11 @@ static int read_bwd_impl(const void *V, const float *R, void *dV, float *dR, con
         // two independent pipelines whose phases drift apart (no faster since phase 1 became straight-line code: an option only)
         const bool half = g_opt.bwd_warps == 4;
         ncw = half ? 4 : 8; wpt = 1; fr = nch;
-    } else if (sg.deferred && !g_opt.bwd_warps && !g_opt.bwd_wpt && nch % 3 == 0 && (nch == 6 || nch == 12 || nch == 24)) {
-        // the deferred form keeps g packed and has registers for 3 fragments per warp: 8 consumer warps, fewer warps
-        // per token to exchange partial dot products between (measured: -1 % at 6 chunks, -6 % at 12)
+    } else if (sg.deferred && !g_opt.bwd_warps && !g_opt.bwd_wpt && (nch == 8 || nch == 16 || nch == 32)) {
+        // the deferred form keeps g packed and has registers for 3 or 4 fragments per warp: 8 consumer warps, fewer warps
+        // per token to exchange partial dot products between (measured: -15 % at 8 chunks, -6 % at 12)
+        ncw = 8; fr = 4; wpt = nch / 4;
+    } else if (sg.deferred && !g_opt.bwd_warps && !g_opt.bwd_wpt && (nch == 6 || nch == 12 || nch == 24)) {
         ncw = 8; fr = 3; wpt = nch / 3;
     } else {
         for (int a = 0; a < 3; ++a) {

@@ -26,6 +26,7 @@
 #define LB_BWD_UNROLL 4
 #endif
 
+
 namespace lb {
 
 // scalar warps per CTA: 2, or 1 in the half-size CTA (4 consumer warps) of which two share an SM
@@ -40,7 +41,8 @@ struct BwdSmemTail {
     float lc[kMaxSources];
     float mass;
     int abort_flag;
-    float xch[2][kBwdMaxNcw];                   // partial g.v of the token's warps, double buffered by source
+    alignas(16) float xch[2][kBwdMaxNcw][4];    // partial g.v of the token's warps (up to 4 sources at a time, read and
+                                                // written as 16-byte vectors), double buffered
     float fin[kBwdMaxNcw];                      // per token: coefficient of the key-scale term of the finalised source
     float fin0[kBwdMaxNcw];                     // ... and of update 0, which the step-1 backward finishes as well
     uint64_t full[kBwdMaxStages];
@@ -48,6 +50,9 @@ struct BwdSmemTail {
     uint64_t sfull[2];
     uint64_t sempty[2];
 };
+
+static_assert(offsetof(BwdSmemTail, xch) % 16 == 0, "the exchange buffers are accessed with 16-byte loads and stores");
+static_assert(offsetof(BwdSmemTail, full) % 8 == 0, "mbarriers are 8-byte objects");
 
 // dynamic shared memory: [stages][tables 2 x 6 x n_pad*BT][gdkq n_pad*BT][dq slots][q: chunks*512/elem floats][tail]
 __host__ __device__ inline int bwd_npad(int n) { return (n + 3) & ~3; }
@@ -259,7 +264,7 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             // is covered by its FMAs instead of stalling the warp.
             auto iter = [&](int i, auto load_tag, auto acc_tag) {
                 constexpr bool LOAD = decltype(load_tag)::value, ACC = decltype(acc_tag)::value;
-                if (WPT > 1 && i >= 1 && i <= n && lane == 0) sts_f32(xch_a + 4u * (((i - 1) & 1) * kBwdMaxNcw + warp), d1);
+                if (WPT > 1 && i >= 1 && i <= n && lane == 0) sts_f32(xch_a + 16u * (((i - 1) & 1) * kBwdMaxNcw + warp), d1);
                 uint4 raw[FR];
                 float x = 0.f;                    // this lane's share of g . v_i, then the warp's
                 if constexpr (LOAD) {
@@ -280,8 +285,8 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     float gd = SOLO ? d1 : d2;
                     if (WPT > 1) {
                         gd = 0.f;
-                        const uint32_t xa = xch_a + 4u * (((i - 2) & 1) * kBwdMaxNcw + t * WPT);
-                        for (int w2 = 0; w2 < WPT; ++w2) gd += lds_f32(xa + 4u * w2);
+                        const uint32_t xa = xch_a + 16u * (((i - 2) & 1) * kBwdMaxNcw + t * WPT);
+                        for (int w2 = 0; w2 < WPT; ++w2) gd += lds_f32(xa + 16u * w2);
                     }
                     if (part == 0 && lane == 0) sts_f32(gk + j4, gd);
                     const float pj = lds_f32(tb + j4), rj = lds_f32(tb + tfl4 + j4);
@@ -343,7 +348,104 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     for (int k = 0; k < FR; ++k) { if constexpr (!SOLO) v2[k] = v1[k]; v1[k] = raw[k]; }
                 }
             };
-            {
+            if constexpr (!SOLO) {
+                // Several warps per token: the sources are taken up to four at a time, in two sweeps over the same ring
+                // stages. Sweep 1 forms this warp's share of the group's dot products; their shuffle reductions run
+                // interleaved, and the token's warps exchange all the partial sums through ONE barrier (instead of one
+                // barrier and one dependent reduction per source). Sweep 2 reads the tiles again from shared memory,
+                // accumulates them and releases the stages. A group is at most half the ring, so that the producer
+                // fetches the next group meanwhile. Every sum is formed in the order of the one-warp-per-token loops.
+                constexpr int GS = 4;
+                const int gs = NS >= 2 * GS ? GS : (NS >= 2 ? NS / 2 : 1);
+                // (one group, its size a compile-time constant: straight-line code, as in the loops below)
+                auto group = [&](int base, int grp, auto m_tag) {
+                    constexpr int m = decltype(m_tag)::value;
+                    const uint32_t xb = xch_a + 16u * ((grp & 1) * kBwdMaxNcw);
+                    float x[GS];
+                    uint32_t sbs[GS];
+                    {
+                        int stj = st; uint32_t phj = ph;
+#pragma unroll
+                        for (int j = 0; j < GS; ++j) {
+                            x[j] = 0.f; sbs[j] = stages_a;
+                            if (j < m) {
+                                if (alive && !mbar_wait(full_a + 8u * stj, phj, wc, kDevWaitFull)) alive = false;
+                                sbs[j] = stages_a + (uint32_t)stj * pitch;
+                                if (++stj == NS) { stj = 0; phj ^= 1u; }
+                                float2 d2a = make_float2(0.f, 0.f), d2b = make_float2(0.f, 0.f);
+#pragma unroll
+                                for (int k = 0; k < FR; ++k) {
+                                    const uint4 raw = valid[k] ? lds_v4(sbs[j] + foff[k]) : zero4;
+                                    if constexpr (PACKG && S::kBytes == 2) {
+                                        // both operands are packed bf16: the dot product straight from the packed registers
+                                        fma_bf16x2(gpk[k].x, raw.x, d2a.x, d2a.y);
+                                        fma_bf16x2(gpk[k].y, raw.y, d2b.x, d2b.y);
+                                        fma_bf16x2(gpk[k].z, raw.z, d2a.x, d2a.y);
+                                        fma_bf16x2(gpk[k].w, raw.w, d2b.x, d2b.y);
+                                    } else {
+                                        float2 vf[P], gf[P];
+                                        S::unpack2(raw, vf);
+                                        load_g(k, gf);
+#pragma unroll
+                                        for (int e = 0; e < P; e += 2) {
+                                            d2a = __ffma2_rn(gf[e], vf[e], d2a);
+                                            d2b = __ffma2_rn(gf[e + 1], vf[e + 1], d2b);
+                                        }
+                                    }
+                                }
+                                x[j] = (d2a.x + d2b.x) + (d2a.y + d2b.y);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                        for (int j = 0; j < GS; ++j) x[j] += __shfl_xor_sync(0xffffffffu, x[j], o);
+                    if (lane == 0) sts_f4(xb + 16u * warp, make_float4(x[0], x[1], x[2], x[3]));
+                    named_bar_sync(bar_id, bar_threads);
+                    float gd[GS] = {0.f, 0.f, 0.f, 0.f};
+                    for (int w2 = 0; w2 < WPT; ++w2) {
+                        const float4 q = lds_f4(xb + 16u * (t * WPT + w2));
+                        gd[0] += q.x; gd[1] += q.y; gd[2] += q.z; gd[3] += q.w;
+                    }
+#pragma unroll
+                    for (int j = 0; j < GS; ++j) {
+                        if (j < m) {
+                            const uint32_t j4 = (uint32_t)(base + j) * BT4;
+                            if (part == 0 && lane == 0) sts_f32(gk + j4, gd[j]);
+                            const float pj = lds_f32(tb + j4), rj = lds_f32(tb + tfl4 + j4);
+                            const float gp = mass * (gd[j] + lds_f32(tb + 2u * tfl4 + j4));
+                            sacc = fmaf(pj, gp, sacc);
+                            const float b = pj * rj, a = b * gp;
+                            const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
+#pragma unroll
+                            for (int k = 0; k < FR; ++k) {
+                                const uint4 raw = valid[k] ? lds_v4(sbs[j] + foff[k]) : zero4;
+                                v2[k] = raw;              // after the last group: source n - 1 (used by phase 2)
+                                float2 vf[P];
+                                S::unpack2(raw, vf);
+#pragma unroll
+                                for (int e = 0; e < P; ++e) {
+                                    A[k][e] = __ffma2_rn(a2, vf[e], A[k][e]);
+                                    B[k][e] = __ffma2_rn(b2, vf[e], B[k][e]);
+                                }
+                            }
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(empty_a + 8u * st);
+                            if (++st == NS) { st = 0; ph ^= 1u; }
+                        }
+                    }
+                };
+                int grp = 0;
+                for (int base = 0; base < n; base += gs, ++grp) {
+                    switch (min(gs, n - base)) {
+                        case 4: group(base, grp, std::integral_constant<int, 4>{}); break;
+                        case 3: group(base, grp, std::integral_constant<int, 3>{}); break;
+                        case 2: group(base, grp, std::integral_constant<int, 2>{}); break;
+                        default: group(base, grp, std::integral_constant<int, 1>{}); break;
+                    }
+                }
+            } else {
                 int i = 0;
                 for (; i < DEPTH; ++i) {                                   // fill: nothing to accumulate yet
                     if (i < n) iter(i, std::true_type{}, std::false_type{});
