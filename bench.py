@@ -609,15 +609,37 @@ def main():
     exchange_us = None
     if world > 1 and w["backward"]:
         qg = torch.randn(N - 1, d, device=dev)
-        for _ in range(5):
-            dist.all_reduce(qg)
-        exchange_us = {"nccl_all_reduce": R.timed(lambda: dist.all_reduce(qg), 50) / 50 * 1e3}
+
+        def per_call_us(fn, reps=20):
+            """Device time of one call: `reps` calls captured as one CUDA graph (no host launch cost between them)."""
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            try:
+                side = torch.cuda.Stream(device=dev)
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    fn()
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for _ in range(reps):
+                        fn()
+                ok = True
+            except Exception:  # noqa: BLE001 -- fall back to eager calls (host-bound: an upper bound)
+                ok, g = False, None
+            if R.all_agree(ok):
+                g.replay()
+                return R.timed(g.replay, 5) / 5 / reps * 1e3, "graph replay of 20 calls"
+            return R.timed(fn, 50) / 50 * 1e3, "back-to-back eager calls (host-bound)"
+        us, how = per_call_us(lambda: dist.all_reduce(qg))
+        exchange_us = {"nccl_all_reduce": us, "nccl_how": how}
         pr = peers.get(id(P.cell)) or P.cell.peer_reduce
         if pr is not None:
-            for _ in range(5):
-                pr.reduce()
-            exchange_us["peer_memory_one_shot"] = R.timed(pr.reduce, 50) / 50 * 1e3
-        exchange_us["what"] = "back-to-back eager calls, device time per call, max over ranks"
+            us, how = per_call_us(pr.reduce)
+            exchange_us.update(peer_memory_one_shot=us, peer_how=how)
+        exchange_us["what"] = "device time per call of the (N-1) x d fp32 sum alone, max over ranks"
         assert FD.device_error() == 0
 
     # ---- the other BASELINE configurations ------------------------------------------------------------------------

@@ -72,11 +72,15 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReducePar
     if (s_ok) {
         const long long lo = (long long)b * p.slice4, hi = min(lo + p.slice4, p.n4);
         for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-            float4 acc = ld_relaxed_sys_f4(p.bufs[0] + 4 * i);
-            for (int r = 1; r < p.world; ++r) {
-                const float4 v = ld_relaxed_sys_f4(p.bufs[r] + 4 * i);
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
+            // every rank's group is requested before the first is used: one NVLink round trip per group, not one per rank
+            float4 v[kMaxPeers];
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+                if (r < p.world) v[r] = ld_relaxed_sys_f4(p.bufs[r] + 4 * i);
+            float4 acc = v[0];
+#pragma unroll
+            for (int r = 1; r < kMaxPeers; ++r)
+                if (r < p.world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
             reinterpret_cast<float4 *>(p.out)[i] = acc;
         }
     }
@@ -87,7 +91,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReducePar
 }  // namespace
 
 int peer_allreduce_ctas(long long n4) {
-    long long g = (n4 + 1023) / 1024;         // up to four 16-byte groups per thread
+    long long g = (n4 + 255) / 256;           // one 16-byte group per thread while the CTAs last
     return (int)(g < 1 ? 1 : (g > kPeerCtas ? kPeerCtas : g));
 }
 
