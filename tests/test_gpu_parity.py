@@ -228,7 +228,7 @@ def test_step_bwd_equals_combine_bwd_plus_the_torch_glue(L, dtype, n_tok, d, n, 
                                                (37, 768, 12, 5, True), (130, 1024, 24, 23, True), (9, 3072, 8, 3, False),
                                                (3, 4096, 6, 4, True), (300, 320, 10, 9, False), (17, 136, 130, 127, True)])
 def test_step_fwd_equals_write_then_read(L, dtype, n_tok, d, N, s, blend):
-    """lb_step_fwd (one launch, no cached scores, online softmax) against lb_write followed by lb_combine_fwd: the
+    """lb_step_fwd (one launch, no cached scores, two sweeps over L2) against lb_write followed by lb_combine_fwd: the
     stored update bit for bit, its key scale, the coefficients and the saved softmax statistics to fp32 round-off,
     the output to fp32 round-off (fp32 rows) or the last bf16 bit; and the zero-query identity bit for bit."""
     n, NQ, beta, lam = s + 1, N - 1, 0.75, 0.25 if blend else 1.0
