@@ -843,8 +843,18 @@ def e2e_leg(R, P, w, args):
         e2e_pass()
     e2e_steps = max(2, min(args.steps, 5))
     e2e_ms = R.timed(e2e_pass, e2e_steps) / e2e_steps
+    # for context: what this box's host link gives a plain pinned-memory copy of one such tensor, back to back
+    torch.cuda.synchronize()
+
+    def raw_copies():
+        for k in range(8):
+            ring[k % len(ring)].copy_(host_D[k % 2], non_blocking=True)
+    raw_copies()
+    h2d_gbs = 8 * n_tok * d * elem / (R.timed(raw_copies, 1) * 1e-3) / 1e9
     return {"value": world * n_tok / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "h2d_gbs_in_pass": h2d / (e2e_ms * 1e-3) / 1e9, "h2d_gbs_plain_copies": h2d_gbs,
+            "note": "bound by the host link: the pass moves its inputs at the rate plain pinned-memory copies reach"}
 
 
 if __name__ == "__main__":

@@ -703,6 +703,10 @@ class FusedStepStk(torch.autograd.Function):
             if stack.peer_reduce is not None:
                 if stack.peer_reduce.shape != (ctx.q_rows, d):
                     raise RuntimeError("delta_attnres stacked read: the peer reduction was built for another query shape")
+                if stack._n_step_nodes != ctx.q_rows:
+                    # a read that went another way hands its query-gradient row to autograd by itself, unsummed
+                    raise RuntimeError("delta_attnres stacked read: the peer reduction of the query gradient needs every "
+                                       f"read of the pass to be a fused step ({stack._n_step_nodes} of {ctx.q_rows} are)")
                 stack._dq = stack.peer_reduce.rows.zero_()
             else:
                 stack._dq = torch.zeros((ctx.q_rows, d), device=dev, dtype=torch.float32)
