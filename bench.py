@@ -854,7 +854,8 @@ def e2e_leg(R, P, w, args):
     return {"value": world * n_tok / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "h2d_gbs_in_pass": h2d / (e2e_ms * 1e-3) / 1e9, "h2d_gbs_plain_copies": h2d_gbs,
-            "note": "bound by the host link: the pass moves its inputs at the rate plain pinned-memory copies reach"}
+            "note": "bound by the host link: compare the rate at which the pass moves its inputs (h2d_gbs_in_pass, with the "
+                    "results going back at the same time) with what plain pinned-memory copies reach on this box"}
 
 
 if __name__ == "__main__":
