@@ -409,6 +409,27 @@ def test_sources_per_stage_do_not_change_a_bit(FD, L, b, t, d, n, dtype):
             assert torch.equal(got[0][key], other[key]), key
 
 
+@pytest.mark.parametrize("b,t,d,n,dtype", [(1, 40, 1536, 11, torch.bfloat16), (1, 24, 3072, 9, torch.bfloat16),
+                                           (1, 33, 2048, 6, torch.bfloat16), (1, 20, 1024, 7, torch.float32),
+                                           (2, 50, 1024, 10, torch.bfloat16)])
+def test_ring_depth_does_not_change_a_bit_in_the_backward(FD, L, b, t, d, n, dtype):
+    """Rows split over several warps per token take their sources in groups of up to four, at most half the TMA ring
+    at a time: with a ring of 2, 3, 5 or 8 stages the groups are 1, 1, 2 and 4 sources, and every sum is still formed in
+    the same order (the one-warp-per-token shape in the list is there for the ring itself)."""
+    ins = cases.read_inputs(b, t, d, n, dtype, seed=3 * n + d)
+    got = []
+    try:
+        for stages in (0, 2, 3, 5, 8):
+            L.set_option("bwd_stages", stages)
+            got.append(run_read_gpu(FD, *ins, False))
+    finally:
+        L.reset_options()
+    for other in got[1:]:
+        for key in ("out", "tc", "dd", "dq", "dcoef"):
+            assert torch.equal(got[0][key], other[key]), key
+    assert L.device_error() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n", [2, 9, 16, 40])
 def test_zero_query_identity_is_bitwise(FD, dtype, n):
