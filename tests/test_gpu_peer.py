@@ -46,12 +46,12 @@ def _call(L, bufs, flags, rank, out):
     return L.lib().lb_peer_allreduce(pb, pf, rank, world, L.ptr(out), out.numel(), L.stream_ptr())
 
 
-@pytest.mark.parametrize("world,n", [(2, 23 * 1024), (4, 5 * 96), (8, 79 * 2048), (16, 4)])
+@pytest.mark.parametrize("world,n", [(1, 64), (2, 23 * 1024), (4, 5 * 96), (8, 79 * 2048), (16, 4)])
 def test_emulated_ranks_sum_in_rank_order(L, world, n):
-    """Rank 1 of `world`, its peers' flags already at a far epoch: the sum over the buffers in rank order, call after
-    call (the call counter lives on the device)."""
+    """The last rank of `world`, its peers' flags already at a far epoch: the sum over the buffers in rank order, call
+    after call (the call counter lives on the device). A world of one is a copy."""
     bufs, flags, words = _blocks(L, world, n)
-    me = 1
+    me = world - 1
     ctas = words // (2 * 16 + 1)               # layout: [2 phases][LB_MAX_PEERS][ctas], then one counter per CTA
     f = flags[me].view(-1)
     for phase in range(2):
