@@ -869,7 +869,7 @@ def test_full_size_properties(FD, d, K, R, b, t):
     Q = torch.randn(N - 1, d, device="cuda", generator=g) * 0.02
     Gu = torch.randn(2, b, t, d, device="cuda", generator=g)
 
-    def run(h0_, D_, Q_, grad):
+    def run(h0_, D_, Q_, grad, lo=0):
         from loopback_b200.cell import LoopDeltaAttnRes
         cell = LoopDeltaAttnRes(d, R, K).cuda()
         with torch.no_grad():
@@ -886,7 +886,7 @@ def test_full_size_properties(FD, d, K, R, b, t):
                 deltas.append(stack.write(s, hs, x))
                 x, coeffs, prior = cell.combine(hs, h0r, deltas, coeffs, prior, l, blk, keys=keys, stack=stack)
                 if grad:
-                    loss = loss + (x.float() * Gu[s % 2, :bb]).sum()
+                    loss = loss + (x.float() * Gu[s % 2, lo:lo + bb]).sum()
             if grad:
                 loss.backward()
         return x.detach(), coeffs.detach(), prior.detach(), (h0r.grad, cell.query.grad) if grad else None
@@ -896,6 +896,14 @@ def test_full_size_properties(FD, d, K, R, b, t):
     assert torch.equal(x_full[:2], x_part) and torch.equal(tc_full[:2], tc_part)
     assert torch.equal(grads_full[0][:2], grads_part[0])
     assert torch.isfinite(grads_full[1]).all() and torch.isfinite(grads_full[0]).all()
+    # (a') the query gradient is a sum over tokens: the slices' gradients add up to the full batch's (fp32 round-off of
+    # a different summation order), and every slice's loop-input gradient is the full one's slice, bit for bit
+    dq_sum = grads_part[1].double()
+    for lo in range(2, b, 2):
+        _, _, _, gp = run(h0[lo:lo + 2], D[:, lo:lo + 2], Q, True, lo)
+        assert torch.equal(grads_full[0][lo:lo + 2], gp[0])
+        dq_sum += gp[1].double()
+    assert float((dq_sum - grads_full[1].double()).abs().max()) < 2e-5 * float(grads_full[1].abs().max())
     assert float((tc_full.sum(-1) - c0.sum()).abs().max()) < 1e-4 * float(c0.sum())
     x_zero, tc_zero, c0z, _ = run(h0, D, torch.zeros_like(Q), False)
     assert torch.equal(tc_zero, c0z.view(1, 1, -1).expand_as(tc_zero))
