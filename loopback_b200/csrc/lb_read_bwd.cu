@@ -820,41 +820,79 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             if (!mbar_wait<true>(sempty_a + 8u * buf, (uint32_t)(((tcount >> 1) & 1) ^ 1), wc, kDevWaitScalarSlot))
                 return;
             const uint32_t tb = tables_a + buf * kBwdTables * tfl4;
-            for (int idx = sw * 32 + lane; idx < BT * n; idx += kBwdScalarWarps * 32) {
-                const int t = idx / n, i = idx - t * n;
-                long long tok = tile * BT + t;
-                if (tok >= p.n_tok) tok = p.n_tok - 1;
-                const float lg = __ldg(p.LG + tok * n + i);
-                const float lse = __ldg(p.LSE + tok), lse0 = __ldg(p.LSE0 + tok);
-                const float cb = p.tc_prev == nullptr ? __ldg(p.cbar + tok * n + i)
+            // (the loads of up to four passes over the tile's (token, source) pairs are all requested before the first
+            // is used: one memory round trip per tile instead of one per pass -- this is what a launch's first tile waits for)
+            constexpr int SU = 4;
+            constexpr int kStride = kBwdScalarWarps * 32;
+            for (int idx0 = sw * 32 + lane; idx0 < BT * n; idx0 += SU * kStride) {
+                float lgv[SU], lsev[SU], lse0v[SU], cbv[SU], gtvv[SU], rv[SU], drpv[SU];
+#pragma unroll
+                for (int u = 0; u < SU; ++u) {
+                    const int idx = idx0 + u * kStride;
+                    lgv[u] = 0.f; lsev[u] = 0.f; lse0v[u] = 0.f; cbv[u] = 0.f; gtvv[u] = 0.f; rv[u] = 1.f; drpv[u] = 0.f;
+                    if (idx < BT * n) {
+                        const int t = idx / n, i = idx - t * n;
+                        long long tok = tile * BT + t;
+                        if (tok >= p.n_tok) tok = p.n_tok - 1;
+                        lgv[u] = __ldg(p.LG + tok * n + i);
+                        lsev[u] = __ldg(p.LSE + tok); lse0v[u] = __ldg(p.LSE0 + tok);
+                        cbv[u] = p.tc_prev == nullptr ? __ldg(p.cbar + tok * n + i)
                                                       : (i < n - 1 ? p.lam * __ldg(p.tc_prev + tok * (n - 1) + i) : p.lam);
-                const float gtv = p.gt ? __ldg(p.gt + tok * n + i) : 0.f;
-                const float r = __ldg(p.R + (long long)i * p.n_tok + tok);
-                const float drp = p.accum ? p.dR[(long long)i * p.n_tok + tok] : 0.f;
-                const float lci = lds_f32(lc_a + 4u * i);
-                const float pi = expf(lg - lse), p0 = expf(lci - lse0);
-                const uint32_t o = tb + 4u * (uint32_t)(i * BT + t);
-                sts_f32(o, pi);
-                sts_f32(o + tfl4, r);
-                sts_f32(o + 2u * tfl4, gtv);
-                sts_f32(o + 3u * tfl4, lds_f32(c0_a + 4u * i) - cb + mass * (pi - p0));
-                sts_f32(o + 4u * tfl4, (lg - lci) / r);
-                sts_f32(o + 5u * tfl4, drp);
+                        gtvv[u] = p.gt ? __ldg(p.gt + tok * n + i) : 0.f;
+                        rv[u] = __ldg(p.R + (long long)i * p.n_tok + tok);
+                        drpv[u] = p.accum ? p.dR[(long long)i * p.n_tok + tok] : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < SU; ++u) {
+                    const int idx = idx0 + u * kStride;
+                    if (idx < BT * n) {
+                        const int t = idx / n, i = idx - t * n;
+                        const float lg = lgv[u], r = rv[u];
+                        const float lci = lds_f32(lc_a + 4u * i);
+                        const float pi = expf(lg - lsev[u]), p0 = expf(lci - lse0v[u]);
+                        const uint32_t o = tb + 4u * (uint32_t)(i * BT + t);
+                        sts_f32(o, pi);
+                        sts_f32(o + tfl4, r);
+                        sts_f32(o + 2u * tfl4, gtvv[u]);
+                        sts_f32(o + 3u * tfl4, lds_f32(c0_a + 4u * i) - cbv[u] + mass * (pi - p0));
+                        sts_f32(o + 4u * tfl4, (lg - lci) / r);
+                        sts_f32(o + 5u * tfl4, drpv[u]);
+                    }
+                }
             }
             if constexpr (DEFER) {
                 // the scalars the earlier backward steps left for the update(s) this step finishes: lanes over tokens
                 const uint32_t ft = ft_a + buf * 4u * ftl4;
-                for (int idx = sw * 32 + lane; idx < BT * J; idx += kBwdScalarWarps * 32) {
-                    const int j = idx / BT, t = idx - j * BT;
-                    long long tok = tile * BT + t;
-                    if (tok >= p.n_tok) tok = p.n_tok - 1;
-                    const long long e = ((long long)(n + j) * p.n_total + (n - 1)) * p.n_tok + tok;
-                    sts_f32(ft + 4u * (uint32_t)idx, __ldg(p.Wt + e));
-                    sts_f32(ft + ftl4 + 4u * (uint32_t)idx, __ldg(p.KQt + e));
-                    if (fin2) {
-                        const long long e0 = (long long)(n + j) * p.n_total * p.n_tok + tok;
-                        sts_f32(ft + 2u * ftl4 + 4u * (uint32_t)idx, __ldg(p.Wt + e0));
-                        sts_f32(ft + 3u * ftl4 + 4u * (uint32_t)idx, __ldg(p.KQt + e0));
+                for (int idx0 = sw * 32 + lane; idx0 < BT * J; idx0 += SU * kStride) {
+                    float wv[SU], kv[SU], w0v[SU], k0v[SU];
+#pragma unroll
+                    for (int u = 0; u < SU; ++u) {
+                        const int idx = idx0 + u * kStride;
+                        wv[u] = 0.f; kv[u] = 0.f; w0v[u] = 0.f; k0v[u] = 0.f;
+                        if (idx < BT * J) {
+                            const int j = idx / BT, t = idx - j * BT;
+                            long long tok = tile * BT + t;
+                            if (tok >= p.n_tok) tok = p.n_tok - 1;
+                            const long long e = ((long long)(n + j) * p.n_total + (n - 1)) * p.n_tok + tok;
+                            wv[u] = __ldg(p.Wt + e); kv[u] = __ldg(p.KQt + e);
+                            if (fin2) {
+                                const long long e0 = (long long)(n + j) * p.n_total * p.n_tok + tok;
+                                w0v[u] = __ldg(p.Wt + e0); k0v[u] = __ldg(p.KQt + e0);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < SU; ++u) {
+                        const int idx = idx0 + u * kStride;
+                        if (idx < BT * J) {
+                            sts_f32(ft + 4u * (uint32_t)idx, wv[u]);
+                            sts_f32(ft + ftl4 + 4u * (uint32_t)idx, kv[u]);
+                            if (fin2) {
+                                sts_f32(ft + 2u * ftl4 + 4u * (uint32_t)idx, w0v[u]);
+                                sts_f32(ft + 3u * ftl4 + 4u * (uint32_t)idx, k0v[u]);
+                            }
+                        }
                     }
                 }
             }
