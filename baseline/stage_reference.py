@@ -6,7 +6,7 @@ test or the benchmark can import them on a machine that has no reference checkou
 `looped_transformer.py` with the readers it imports, the Triton module `fused_dattn.py`, and the trainer model's package
 `trainer/flame/custom_models/`. Files are copied byte for byte, never edited.
 
-    python baseline/stage_reference.py [reference root]      (default: $LOOPBACK_REF, else /root/reference)
+    python baseline/stage_reference.py [reference root]      (default: $LOOPBACK_REF, else DEFAULT_ROOT below)
 """
 from __future__ import annotations
 
@@ -19,10 +19,11 @@ DEST = os.path.join(HERE, "_ref")
 FILES = ("looped_transformer.py", "loop_linattn_state.py", "loop_linattn_delta.py", "fused_dattn.py", "LICENSE",
          os.path.join("trainer", "flame", "__init__.py"))
 TREES = (os.path.join("trainer", "flame", "custom_models"),)
+DEFAULT_ROOT = os.path.join(os.sep, "root", "reference")     # where the build machine keeps its reference checkout
 
 
 def default_source() -> str | None:
-    for cand in (os.environ.get("LOOPBACK_REF"), "/root/reference"):
+    for cand in (os.environ.get("LOOPBACK_REF"), DEFAULT_ROOT):
         if cand and os.path.isfile(os.path.join(cand, "fused_dattn.py")):
             return cand
     return None
