@@ -504,16 +504,21 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
             if (WPT > 1) named_bar_sync(bar_id, bar_threads); else __syncwarp();
 
             // ---- phase 2: the gradient of every source
-            float2 q2[FR][P];
-#pragma unroll
-            for (int k = 0; k < FR; ++k) {
+            // (the step's own query row: held in registers where every source's update uses it; the deferred form uses it
+            // once per finished update and reads it where it is used)
+            auto load_q = [&](int k, float2 (&qf)[P]) {
                 const int col = (chunk0 + k) * BW + lane * VEC;
 #pragma unroll
                 for (int e4 = 0; e4 < V4; ++e4) {
                     const float4 q4 = lds_f4(qsm_a + 16u * (col / 4 + e4));
-                    q2[k][2 * e4] = make_float2(q4.x, q4.y);
-                    q2[k][2 * e4 + 1] = make_float2(q4.z, q4.w);
+                    qf[2 * e4] = make_float2(q4.x, q4.y);
+                    qf[2 * e4 + 1] = make_float2(q4.z, q4.w);
                 }
+            };
+            float2 q2[DEFER ? 1 : FR][P];
+            if constexpr (!DEFER) {
+#pragma unroll
+                for (int k = 0; k < FR; ++k) load_q(k, q2[k]);
             }
             if constexpr (DEFER) {
                 // The finished gradient of an update, formed in one go:
@@ -530,12 +535,13 @@ read_bwd_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__
                     float2 acc[FR][P];
 #pragma unroll
                     for (int k = 0; k < FR; ++k) {
-                        float2 gf[P], vf[P];
+                        float2 gf[P], vf[P], qf[P];
                         load_g(k, gf);
+                        load_q(k, qf);
                         S::unpack2(vfr[k], vf);
 #pragma unroll
                         for (int e = 0; e < P; ++e)
-                            acc[k][e] = __ffma2_rn(kf2, vf[e], __ffma2_rn(w2, gf[e], __fmul2_rn(kq2, q2[k][e])));
+                            acc[k][e] = __ffma2_rn(kf2, vf[e], __ffma2_rn(w2, gf[e], __fmul2_rn(kq2, qf[e])));
                     }
                     for (int j = 0; j < J; ++j) {
                         if (alive && !mbar_wait(full_a + 8u * st, ph, wc, kDevWaitFull)) alive = false;
