@@ -15,9 +15,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libloopback_b200.so")
-SOURCES = ("lb_api.cu", "lb_write.cu", "lb_write_mma.cu", "lb_read_fwd.cu", "lb_read_bwd.cu", "lb_step.cu",
+SOURCES = ("lb_api.cu", "lb_write.cu", "lb_write_mma.cu", "lb_read_fwd.cu", "lb_read_bwd.cu", "lb_read_bwd_f32.cu", "lb_step.cu",
            "lb_noalloc.cu", "lb_peer.cu")
-HEADERS = ("lb_common.cuh", "lb_kernels.h", os.path.join("..", "..", "include", "loopback_b200.h"))
+HEADERS = ("lb_common.cuh", "lb_kernels.h", "lb_read_bwd_impl.cuh", os.path.join("..", "..", "include", "loopback_b200.h"))
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-ccbin", "g++",
          "--expt-relaxed-constexpr"]
